@@ -3,12 +3,17 @@
 Storage is paged: a page holds `PAGE` consecutive tokens of one sequence, for every user of its
 group, laid out [page, kv head, token, dim] so that one head's keys of a page are contiguous.
 A user is one mixer of one entry of the model's run order.  Users that need the same head
-count, key width, value width and ring length form a group and share one page numbering; a group
-that keeps every key and a group that keeps a window have pools and page tables of their own,
-and a window group's pool holds no more pages than its rings can use.
+count, key width, value width, ring length and number of pinned pages form a group and share one
+page numbering; a group that keeps every key and a group that keeps a window have pools and page
+tables of their own, and a window group's pool holds no more pages than its rings can use.  A
+window group whose users also keep a sequence's first tokens for good holds those in `pinned`
+pages ahead of the ring: logical page lp < pinned sits at table entry lp, a later one at entry
+pinned + (lp - pinned) % ring.
 
 Beside the pages each slot owns a fixed-size float32 state row per user that asks for one
-(`Mixer.state_size()`), zeroed when the slot is acquired.
+(`Mixer.state_size()`), zeroed when the slot is acquired, and `token_state` int32 values for the
+embedding part if it carries something from step to step (set to -1 then).
+
 """
 from __future__ import annotations
 
@@ -42,6 +47,13 @@ def ring_pages(window: Optional[int]) -> Optional[int]:
     return -(-(window - 1) // PAGE) + 1
 
 
+def pinned_pages(window: Optional[int], keep_first: int) -> int:
+    """Pages ahead of the ring that hold a sequence's first `keep_first` tokens for good (none when every key is kept)."""
+    if window is None or keep_first <= 0:
+        return 0
+    return -(-keep_first // PAGE)
+
+
 @dataclass
 class KVView:
     """What a mixer sees of the cache in one step: its call's pools and the batch's page table."""
@@ -50,11 +62,12 @@ class KVView:
     page_table: torch.Tensor        # int32 [n_seqs, width]
     ring: int
     writable: bool
+    pinned: int = 0                 # pages ahead of the ring that are never overwritten
 
 
 class PagedCache:
     def __init__(self, needs: List[Optional[KVNeed]], cache_of: List[Optional[int]], state_sizes: List[int],
-                 config: CacheConfig, dtype: torch.dtype, device, allocate: bool = True):
+                 config: CacheConfig, dtype: torch.dtype, device, allocate: bool = True, token_state: int = 0):
         """needs[u], state_sizes[u]: what user u (a mixer of the run order) asks for; cache_of[u]:
         an earlier user whose keys and values user u reads instead of keeping its own."""
         self.config, self.dtype, self.device = config, dtype, torch.device(device)
@@ -87,7 +100,8 @@ class PagedCache:
                 self.call_group.append(None)
                 self.call_entry.append(None)
                 continue
-            key = (need.num_kv_heads, need.key_dim, need.value_dim, ring_pages(need.window))
+            key = (need.num_kv_heads, need.key_dim, need.value_dim, ring_pages(need.window),
+                   pinned_pages(need.window, need.keep_first))
             if key not in self.group_keys:
                 self.group_keys.append(key)
                 entries_per_group.append(0)
@@ -96,9 +110,11 @@ class PagedCache:
             self.call_entry.append(entries_per_group[g])
             entries_per_group[g] += 1
         self.rings = [k[3] for k in self.group_keys]
-        # a sequence never holds more pages of a window group than its ring has
-        self.group_pages = [n_pages if r is None else min(n_pages, r * self.n_slots) for r in self.rings]
-        self.book = SlotBook(self.n_slots, self.group_pages, self.rings, PAGE)
+        self.pinned = [k[4] for k in self.group_keys]
+        # a sequence never holds more pages of a window group than its ring and its pinned pages
+        self.group_pages = [n_pages if r is None else min(n_pages, (r + p) * self.n_slots)
+                            for r, p in zip(self.rings, self.pinned)]
+        self.book = SlotBook(self.n_slots, self.group_pages, self.rings, PAGE, self.pinned)
         # ---- storage
         self.k_pools: List[torch.Tensor] = []
         self.v_pools: List[torch.Tensor] = []
@@ -106,13 +122,17 @@ class PagedCache:
         self.state_sizes = list(state_sizes)
         self._guards: List[tuple] = []            # (what, raw allocation) of every guarded tensor
         if allocate:
-            for g, ((nkvh, dk, dv, _), n_entries, pages) in enumerate(zip(self.group_keys, entries_per_group, self.group_pages)):
+            for g, ((nkvh, dk, dv, _, _), n_entries, pages) in enumerate(zip(self.group_keys, entries_per_group, self.group_pages)):
                 self.k_pools.append(self._zeros(f"keys of group {g}", (n_entries, pages, nkvh, PAGE, dk), dtype))
                 self.v_pools.append(self._zeros(f"values of group {g}", (n_entries, pages, nkvh, PAGE, dv), dtype)
                                     if dv > 0 else None)
             for c, n in enumerate(state_sizes):
                 if n > 0:
                     self.state[c] = self._zeros(f"state of user {c}", (self.n_slots, n), torch.float32)
+        self.token_state: Optional[torch.Tensor] = None
+        if allocate and token_state > 0:
+            self.token_state = self._zeros("token state", (self.n_slots, token_state), torch.int32)
+            self.token_state.fill_(-1)
         diagnostics.log.info("cache: %d pages of %d tokens, %d slots, groups %s, %.1f MB", n_pages, PAGE, self.n_slots,
                              [(k, p) for k, p in zip(self.group_keys, self.group_pages)],
                              sum(p.numel() * p.element_size() for p in self.k_pools + self.v_pools if p is not None) / 1e6)
@@ -135,6 +155,8 @@ class PagedCache:
         slot = self.book.acquire()
         for st in self.state.values():
             st[slot].zero_()
+        if self.token_state is not None:
+            self.token_state[slot].fill_(-1)
         return slot
 
     def release(self, slot: int) -> None:
@@ -177,7 +199,7 @@ class PagedCache:
         e = self.call_entry[call]
         v = self.v_pools[g]
         return KVView(self.k_pools[g][e], v[e] if v is not None else None, table, self.ring_of(g, table.shape[1]),
-                      writable=self.call_owner[call] is None)
+                      writable=self.call_owner[call] is None, pinned=self.pinned[g])
 
 
 __all__ = ["PAGE", "CacheConfig", "CacheError", "CacheFull", "KVView", "PagedCache", "ring_pages"]

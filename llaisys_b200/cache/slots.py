@@ -63,12 +63,18 @@ class SlotBook:
     groups: list of (ring_pages or None).  A group with ring None keeps every key: a sequence of
     n tokens holds ceil(n / page) pages there.  A group with a ring keeps the last pages only:
     a sequence holds min(ceil(n / page), ring) pages, logical page lp sitting at entry lp % ring.
+    pinned: per group, pages ahead of the ring that hold the sequence's first tokens for good: a sequence
+    holds min(ceil(n / page), pinned + ring) pages, logical page lp < pinned at entry lp, a later one at
+    entry pinned + (lp - pinned) % ring.
     """
 
-    def __init__(self, n_slots: int, pages_per_group: List[int], rings: List[int | None], page: int):
+    def __init__(self, n_slots: int, pages_per_group: List[int], rings: List[int | None], page: int,
+                 pinned: List[int] | None = None):
         assert len(pages_per_group) == len(rings)
         self.page = page
         self.rings = list(rings)
+        self.pinned = list(pinned) if pinned is not None else [0] * len(rings)
+        assert len(self.pinned) == len(self.rings)
         self.slots = FreeList(n_slots, "slot")
         self.pools = [FreeList(n, f"page of group {g}") for g, n in enumerate(pages_per_group)]
         self.seqs: Dict[int, Sequence] = {}
@@ -100,7 +106,7 @@ class SlotBook:
     def pages_needed(self, group: int, length: int) -> int:
         n = -(-length // self.page)
         ring = self.rings[group]
-        return n if ring is None else min(n, ring)
+        return n if ring is None else min(n, ring + self.pinned[group])
 
     def reserve(self, slot: int, n_new: int) -> None:
         """Makes room for n_new more tokens in every group, or raises CacheFull and changes nothing."""
@@ -142,8 +148,9 @@ class SlotBook:
                 pages = seq.pages[g]
                 if len(pages) < self.pages_needed(g, seq.length):
                     bad.append(f"slot {slot} holds {len(pages)} pages of group {g}, too few for {seq.length} tokens")
-                if self.rings[g] is not None and len(pages) > self.rings[g]:
-                    bad.append(f"slot {slot} holds {len(pages)} pages of group {g}, more than its ring of {self.rings[g]}")
+                if self.rings[g] is not None and len(pages) > self.rings[g] + self.pinned[g]:
+                    bad.append(f"slot {slot} holds {len(pages)} pages of group {g}, more than its ring of {self.rings[g]}"
+                               + (f" and {self.pinned[g]} pinned" if self.pinned[g] else ""))
                 for pg in pages:
                     if not (0 <= pg < pool.n):
                         bad.append(f"slot {slot} lists page {pg} of group {g}, outside the pool (0..{pool.n - 1})")

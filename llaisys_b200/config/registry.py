@@ -24,6 +24,8 @@ def known_architectures() -> list[str]:
 
 def config_from_dict(d: dict):
     archs = d.get("architectures")
+    if isinstance(d.get("architecture"), str) and not archs:
+        archs = [d["architecture"]]                  # some configurations name their one architecture in the singular
     if not archs or not isinstance(archs, (list, tuple)):
         raise ConfigError(f"config.json has no 'architectures' list; known architectures: {known_architectures()}")
     name = archs[0]

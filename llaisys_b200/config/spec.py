@@ -19,6 +19,10 @@ class PartSpec:
     prefix: str = ""
 
     def tensor_name(self, local: str) -> str:
+        """The file's name of the part's tensor `local`; an empty local name is the prefix itself (a part whose one
+        tensor carries the part's own name)."""
+        if not local:
+            return self.prefix
         return f"{self.prefix}.{local}" if self.prefix else local
 
 

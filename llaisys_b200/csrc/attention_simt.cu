@@ -5,7 +5,10 @@
 // Formula (src/ops/self_attention/cpu/self_attention_cpu.cpp:28-112 of xsmccc/llaisys): for a
 // query at absolute position p of head h, scores s_t = (q . k_t) * scale over the keys t of kv
 // head h / (nh / nkvh) with t <= p; softmax with the maximum subtracted; out = sum_t p_t v_t.
-// A window W > 0 (not in that project) further restricts the keys to p - W < t <= p.
+// A window W > 0 (not in that project) further restricts the keys to p - W < t <= p; with keep_first F > 0
+// the keys t < F stay visible behind the window (at their true positions).  With `sink` the softmax has one
+// more term of score 0 that carries no value: weights e^{s_t} / (1 + sum e^{s_t}).  Values may have a width
+// of their own (-DLLB_VALUE_DIM, default the head size).
 //
 // Keys are walked in tiles of one cache page with an online softmax, so nothing of size
 // [queries, keys] is ever stored.
@@ -22,20 +25,25 @@
 #error "compile with -DLLB_HEAD_DIM=<head size>"
 #endif
 
-constexpr int DH = LLB_HEAD_DIM;
+#ifndef LLB_VALUE_DIM
+#define LLB_VALUE_DIM LLB_HEAD_DIM
+#endif
+
+constexpr int DH = LLB_HEAD_DIM;     // query / key width
+constexpr int DV = LLB_VALUE_DIM;    // value and output width
 constexpr int ROWS = 32;            // query rows of a block
 constexpr int WARPS = 4;
 constexpr int RPW = ROWS / WARPS;   // rows of a warp
-constexpr int DPL = (DH + 31) / 32; // output dims of a lane
+constexpr int DPL = (DV + 31) / 32; // output dims of a lane
 
 struct AttnParams {
     const void* q;        // packed projections [T, row_stride]; query head h at column h * DH
     const void* k_new;    // the same buffer at its first key column
     const void* v_new;    // the same buffer at its first value column
     int row_stride;
-    void* out;            // [T, nh * DH]
+    void* out;            // [T, nh * DV]
     const void* kpool;    // [pages, nkvh, LLB_PAGE, DH]
-    const void* vpool;
+    const void* vpool;    // [pages, nkvh, LLB_PAGE, DV]
     const int* page_table;  // [B, table_stride]
     int table_stride;
     int ring;
@@ -46,8 +54,11 @@ struct AttnParams {
     int all_from_cache;   // prefill only: the step's own keys are already in the cache (a call that
                           // reads another call's cache); read nothing from k_new / v_new
     int n_splits;         // decode only
-    float* part_o;        // decode only: [B, nh, n_splits, DH]
+    float* part_o;        // decode only: [B, nh, n_splits, DV]
     float* part_ml;       // decode only: [B, nh, n_splits, 2]
+    int keep_first;       // with a window: keys before this position stay visible
+    int pinned;           // pages ahead of the ring that are never overwritten
+    int sink;             // the softmax's denominator has one more term e^0
 };
 
 template <typename T, bool DECODE>
@@ -55,8 +66,8 @@ __global__ void __launch_bounds__(WARPS * 32) attn_kernel(AttnParams p) {
     extern __shared__ float smem[];
     float* Qs = smem;                        // [ROWS][DH]
     float* Ks = Qs + ROWS * DH;              // [LLB_PAGE][DH + 1]
-    float* Vs = Ks + LLB_PAGE * (DH + 1);    // [LLB_PAGE][DH]
-    float* Ps = Vs + LLB_PAGE * DH;          // [WARPS][LLB_PAGE]
+    float* Vs = Ks + LLB_PAGE * (DH + 1);    // [LLB_PAGE][DV]
+    float* Ps = Vs + LLB_PAGE * DV;          // [WARPS][LLB_PAGE]
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int b = blockIdx.z;
@@ -95,21 +106,24 @@ __global__ void __launch_bounds__(WARPS * 32) attn_kernel(AttnParams p) {
         Qs[r * DH + d] = to_f32(qbase[(size_t)tok * p.row_stride + head * DH + d]);
     }
 
-    // ---- key tiles of this block
+    // ---- key tiles of this block: the tiles of the kept first keys that lie before the window's, then the window's
+    const int keep = p.window > 0 ? p.keep_first : 0;
     int key_lo = p.window > 0 ? max(0, first_pos - p.window + 1) : 0;
-    int tile_lo = key_lo / LLB_PAGE, tile_hi = last_pos / LLB_PAGE + 1;
+    const int tile_lo = key_lo / LLB_PAGE, tile_hi = last_pos / LLB_PAGE + 1;
+    const int n_kept = min((keep + LLB_PAGE - 1) / LLB_PAGE, tile_lo);
+    int it_lo = 0, it_hi = n_kept + tile_hi - tile_lo;        // tile it: it < n_kept ? it : tile_lo + it - n_kept
     if (DECODE) {
-        int n_tiles = tile_hi - tile_lo;
-        int chunk = (n_tiles + p.n_splits - 1) / p.n_splits;
-        tile_lo = tile_lo + blockIdx.x * chunk;
-        tile_hi = min(tile_hi, tile_lo + chunk);
+        int chunk = (it_hi + p.n_splits - 1) / p.n_splits;
+        it_lo = blockIdx.x * chunk;
+        it_hi = min(it_hi, it_lo + chunk);
     }
+    const bool with_sink = p.sink && (!DECODE || blockIdx.x == 0);
 
     float m[RPW], l[RPW], o[RPW][DPL];
 #pragma unroll
     for (int i = 0; i < RPW; ++i) {
-        m[i] = -INFINITY;
-        l[i] = 0.f;
+        m[i] = with_sink ? 0.f : -INFINITY;
+        l[i] = with_sink ? 1.f : 0.f;
 #pragma unroll
         for (int e = 0; e < DPL; ++e) o[i][e] = 0.f;
     }
@@ -119,25 +133,32 @@ __global__ void __launch_bounds__(WARPS * 32) attn_kernel(AttnParams p) {
     const T* knew = (const T*)p.k_new;
     const T* vnew = (const T*)p.v_new;
 
-    for (int tile = tile_lo; tile < tile_hi; ++tile) {
+    for (int it = it_lo; it < it_hi; ++it) {
+        const int tile = it < n_kept ? it : tile_lo + it - n_kept;
         __syncthreads();                     // previous tile fully consumed (and Qs written)
         for (int i = tid; i < LLB_PAGE * DH; i += WARPS * 32) {
             int j = i / DH, d = i - j * DH;
             int kp = tile * LLB_PAGE + j;
-            float kv = 0.f, vv = 0.f;
-            if (kp >= key_lo && kp <= last_pos) {
-                if (!DECODE && !p.all_from_cache && kp >= len_before) {
-                    size_t off = (size_t)(tok0 + kp - len_before) * p.row_stride + kvh * DH + d;
-                    kv = to_f32(knew[off]);
-                    vv = to_f32(vnew[off]);
-                } else {
-                    size_t off = paged_row(table, p.ring, kp, kvh, p.nkvh, DH) + d;
-                    kv = to_f32(kpool[off]);
-                    vv = to_f32(vpool[off]);
-                }
+            float kv = 0.f;
+            if ((kp >= key_lo || kp < keep) && kp <= last_pos) {
+                if (!DECODE && !p.all_from_cache && kp >= len_before)
+                    kv = to_f32(knew[(size_t)(tok0 + kp - len_before) * p.row_stride + kvh * DH + d]);
+                else
+                    kv = to_f32(kpool[paged_row(table, p.ring, kp, kvh, p.nkvh, DH, p.pinned) + d]);
             }
             Ks[j * (DH + 1) + d] = kv;
-            Vs[j * DH + d] = vv;
+        }
+        for (int i = tid; i < LLB_PAGE * DV; i += WARPS * 32) {
+            int j = i / DV, d = i - j * DV;
+            int kp = tile * LLB_PAGE + j;
+            float vv = 0.f;
+            if ((kp >= key_lo || kp < keep) && kp <= last_pos) {
+                if (!DECODE && !p.all_from_cache && kp >= len_before)
+                    vv = to_f32(vnew[(size_t)(tok0 + kp - len_before) * p.row_stride + kvh * DV + d]);
+                else
+                    vv = to_f32(vpool[paged_row(table, p.ring, kp, kvh, p.nkvh, DV, p.pinned) + d]);
+            }
+            Vs[j * DV + d] = vv;
         }
         __syncthreads();
 #pragma unroll
@@ -157,7 +178,7 @@ __global__ void __launch_bounds__(WARPS * 32) attn_kernel(AttnParams p) {
                 s1 = fmaf(qv, k1[d], s1);
             }
             int kp0 = tile * LLB_PAGE + lane, kp1 = kp0 + 32;
-            bool v0 = kp0 >= lo && kp0 <= pos, v1 = kp1 >= lo && kp1 <= pos;
+            bool v0 = (kp0 >= lo || kp0 < keep) && kp0 <= pos, v1 = (kp1 >= lo || kp1 < keep) && kp1 <= pos;
             s0 = v0 ? s0 * p.scale : -INFINITY;
             s1 = v1 ? s1 * p.scale : -INFINITY;
             float m_new = fmaxf(m[i], warp_max(fmaxf(s0, s1)));
@@ -174,10 +195,10 @@ __global__ void __launch_bounds__(WARPS * 32) attn_kernel(AttnParams p) {
 #pragma unroll
             for (int e = 0; e < DPL; ++e) {
                 int d = lane + e * 32;
-                if (d < DH) {
+                if (d < DV) {
                     float acc = o[i][e] * alpha;
 #pragma unroll 8
-                    for (int j = 0; j < LLB_PAGE; ++j) acc = fmaf(ps[j], Vs[j * DH + d], acc);
+                    for (int j = 0; j < LLB_PAGE; ++j) acc = fmaf(ps[j], Vs[j * DV + d], acc);
                     o[i][e] = acc;
                 }
             }
@@ -191,19 +212,19 @@ __global__ void __launch_bounds__(WARPS * 32) attn_kernel(AttnParams p) {
         if (r >= n_rows) continue;
         int tok = row_tok0 + (DECODE ? 0 : r), head = row_head0 + (DECODE ? r : 0);
         if (!DECODE || p.n_splits == 1) {
-            T* out = (T*)p.out + (size_t)tok * p.nh * DH + head * DH;
+            T* out = (T*)p.out + (size_t)tok * p.nh * DV + head * DV;
             float inv = 1.0f / l[i];
 #pragma unroll
             for (int e = 0; e < DPL; ++e) {
                 int d = lane + e * 32;
-                if (d < DH) out[d] = from_f32<T>(o[i][e] * inv);
+                if (d < DV) out[d] = from_f32<T>(o[i][e] * inv);
             }
         } else {
             size_t slot = ((size_t)b * p.nh + head) * p.n_splits + blockIdx.x;
 #pragma unroll
             for (int e = 0; e < DPL; ++e) {
                 int d = lane + e * 32;
-                if (d < DH) p.part_o[slot * DH + d] = o[i][e];
+                if (d < DV) p.part_o[slot * DV + d] = o[i][e];
             }
             if (lane == 0) {
                 p.part_ml[slot * 2] = m[i];
@@ -229,18 +250,18 @@ __global__ void attn_combine_kernel(T* __restrict__ out, const float* __restrict
         if (ms != -INFINITY) L += part_ml[(base + s) * 2 + 1] * expf(ms - M);
     }
     int tok = seq_start[b];
-    for (int d = threadIdx.x; d < DH; d += blockDim.x) {
+    for (int d = threadIdx.x; d < DV; d += blockDim.x) {
         float acc = 0.f;
         for (int s = 0; s < n_splits; ++s) {
             float ms = part_ml[(base + s) * 2];
-            if (ms != -INFINITY) acc += part_o[(base + s) * DH + d] * expf(ms - M);
+            if (ms != -INFINITY) acc += part_o[(base + s) * DV + d] * expf(ms - M);
         }
-        out[(size_t)tok * nh * DH + head * DH + d] = from_f32<T>(acc / L);
+        out[(size_t)tok * nh * DV + head * DV + d] = from_f32<T>(acc / L);
     }
 }
 
 static size_t attn_smem_bytes() {
-    return (size_t)(ROWS * DH + LLB_PAGE * (DH + 1) + LLB_PAGE * DH + WARPS * LLB_PAGE) * sizeof(float);
+    return (size_t)(ROWS * DH + LLB_PAGE * (DH + 1) + LLB_PAGE * DV + WARPS * LLB_PAGE) * sizeof(float);
 }
 
 template <typename T, bool DECODE>

@@ -606,5 +606,202 @@ LLB_API int llb_dense_binary(void* out, const void* a, const void* b, int dtype,
     return llb_status();
 }
 
+// ------------------------------------------------------------------ scaled embedding + hashed pair embedding
+// out[t] = table[id_t] * scale + pair_table[r_t].  r_t is the hash (id_{t-1} * mul_prev + id_t * mul_cur) mod buckets of
+// the token and the one before it in its sequence; a sequence's first token (position 0) takes row `buckets`, the table's
+// last.  The token before the first one of a step lives in `last` (int32 [slots, 2]: token, its position), which the
+// block of a sequence's first token of the step reads and then overwrites with the step's last token of that sequence.
+// A `last` entry that is not the position just before (a step that was run twice) sets err = 3.  pair_table null: no
+// pair term and no state.
+template <typename TW>
+__global__ void __launch_bounds__(256)
+embedding_pair_kernel(float* __restrict__ out, const TW* __restrict__ table, const TW* __restrict__ pair_table,
+                      const int* __restrict__ ids, const int* __restrict__ tok_pos, const int* __restrict__ tok_seq,
+                      const int* __restrict__ seq_start, const int* __restrict__ seq_slot, int* __restrict__ last,
+                      int H, int V, float scale, long long buckets, long long mul_prev, long long mul_cur, int* err) {
+    __shared__ int prev_s;
+    llb_grid_dependency_sync();
+    const int t = blockIdx.x, id = ids[t];
+    const bool ok = id >= 0 && id < V;
+    if (!ok && threadIdx.x == 0) atomicExch(err, 1);
+    long long prow = -1;
+    if (pair_table) {
+        const int pos = tok_pos[t], s = tok_seq[t], start = seq_start[s];
+        if (threadIdx.x == 0) {
+            int prev = -1;
+            if (t > start) prev = ids[t - 1];
+            else {
+                int* st = last + 2 * (size_t)seq_slot[s];
+                if (pos > 0) {
+                    prev = st[0];
+                    if (st[1] != pos - 1) atomicExch(err, 3);
+                }
+                const int end = seq_start[s + 1] - 1;
+                st[0] = ids[end];
+                st[1] = pos + (end - start);
+            }
+            prev_s = prev;
+        }
+        __syncthreads();
+        const int prev = prev_s;
+        if (pos == 0) prow = buckets;
+        else if (prev >= 0 && prev < V && ok) {
+            long long h = ((long long)prev * mul_prev + (long long)id * mul_cur) % buckets;
+            prow = h < 0 ? h + buckets : h;
+        }
+    }
+    const TW* row = table + (size_t)(ok ? id : 0) * H;
+    const TW* pr = prow >= 0 ? pair_table + (size_t)prow * H : nullptr;
+    for (int j = threadIdx.x; j < H; j += blockDim.x) {
+        float v = ok ? to_f32(row[j]) * scale : 0.f;
+        if (pr) v += to_f32(pr[j]);
+        out[(size_t)t * H + j] = v;
+    }
+}
+
+LLB_API int llb_embedding_pair(float* out, const void* table, const void* pair_table, int table_dtype, const int* ids,
+                               const int* tok_pos, const int* tok_seq, const int* seq_start, const int* seq_slot, int* last,
+                               int T, int H, int V, float scale, long long buckets, long long mul_prev, long long mul_cur,
+                               int* err, cudaStream_t stream) {
+    if (T == 0) return 0;
+    if (pair_table && buckets <= 0) return (int)cudaErrorInvalidValue;
+    LLB_DISPATCH_DTYPE(table_dtype, TW,
+        llb_launch(embedding_pair_kernel<TW>, dim3(T), dim3(256), 0, stream, out, (const TW*)table, (const TW*)pair_table, ids,
+                   tok_pos, tok_seq, seq_start, seq_slot, last, H, V, scale, buckets, mul_prev, mul_cur, err));
+    return llb_status();
+}
+
+// ------------------------------------------------------------------ one root mean square, several weights
+// out_i[r] = x[r] / sqrt(mean(x[r]^2) + eps) * w_i for i < n (n = 1 or 2): the norms of the branches of a layer
+// whose branches all read the same stream.  x is the float32 stream and is not written.
+template <typename TW, typename TO>
+__global__ void __launch_bounds__(256)
+rmsnorm_multi_kernel(const float* __restrict__ x, const TW* __restrict__ w0, const TW* __restrict__ w1,
+                     TO* __restrict__ out0, TO* __restrict__ out1, int H, float eps) {
+    __shared__ float red[8];
+    llb_grid_dependency_sync();
+    const int r = blockIdx.x, tid = threadIdx.x;
+    const float* row = x + (size_t)r * H;
+    float ss = 0.f;
+    for (int j = tid; j < H; j += 256) {
+        float v = row[j];
+        ss += v * v;
+    }
+    ss = warp_sum(ss);
+    if ((tid & 31) == 0) red[tid >> 5] = ss;
+    __syncthreads();
+    float tot = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) tot += red[i];
+    const float inv = 1.0f / sqrtf(tot / (float)H + eps);
+    for (int j = tid; j < H; j += 256) {
+        const float v = row[j] * inv;
+        out0[(size_t)r * H + j] = from_f32<TO>(v * to_f32(w0[j]));
+        if (out1) out1[(size_t)r * H + j] = from_f32<TO>(v * to_f32(w1[j]));
+    }
+}
+
+LLB_API int llb_rmsnorm_multi(const float* x, const void* w0, const void* w1, int w_dtype, void* out0, void* out1,
+                              int out_dtype, int R, int H, float eps, cudaStream_t stream) {
+    if (R == 0) return 0;
+    LLB_DISPATCH_DTYPE(w_dtype, TW, {
+        LLB_DISPATCH_DTYPE(out_dtype, TO, {
+            llb_launch(rmsnorm_multi_kernel<TW, TO>, dim3(R), dim3(256), 0, stream, x, (const TW*)w0, (const TW*)w1,
+                       (TO*)out0, (TO*)out1, H, eps);
+        });
+    });
+    return llb_status();
+}
+
+// ------------------------------------------------------------------ rotation of a head's leading dimensions + cache append
+// proj is a packed projection output [T, row_stride]: nh query heads of dk elements; then, when the layer projects keys
+// and values of its own (nkvh > 0), nkvh key heads of dk and nkvh value heads of dv elements.  The first `rot` dimensions
+// of every query and key head are rotated in pairs (j, j + rot/2) by the angle of cos_t/sin_t [rows, rot/2] at the
+// token's position; the dimensions from `rot` on pass unchanged.  With APPEND the (rotated) keys and the values are
+// written to the token's row of the paged cache (ring of `ring` pages behind `pinned` pages that are never overwritten).
+template <typename T, bool APPEND>
+__global__ void __launch_bounds__(128)
+rope_lead_append_kernel(T* __restrict__ proj, int row_stride, int nh, int nkvh, int dk, int dv, int rot,
+                        const float* __restrict__ cos_t, const float* __restrict__ sin_t, int table_rows,
+                        const int* __restrict__ tok_pos, const int* __restrict__ tok_seq,
+                        const int* __restrict__ seq_start, const int* __restrict__ seq_len_before,
+                        T* __restrict__ kpool, T* __restrict__ vpool, const int* __restrict__ page_table,
+                        int table_stride, int ring, int pinned, int* err) {
+    const int t = blockIdx.x, pos = tok_pos[t], half = rot >> 1;
+    const int* table = nullptr;
+    bool store = false;
+    if (APPEND) {
+        const int s = tok_seq[t];
+        table = page_table + (size_t)s * table_stride;
+        const int last = seq_len_before[s] + (seq_start[s + 1] - seq_start[s]) - 1;
+        store = paged_survives(pos / LLB_PAGE, last / LLB_PAGE, ring, pinned);
+    }
+    if (half > 0 && (pos < 0 || pos >= table_rows)) {
+        if (threadIdx.x == 0) atomicExch(err, 2);
+        return;
+    }
+    llb_grid_dependency_sync();
+    T* row = proj + (size_t)t * row_stride;
+    for (int i = threadIdx.x; i < (nh + nkvh) * half; i += blockDim.x) {
+        const int h = i / half, j = i - h * half;
+        const float c = cos_t[(size_t)pos * half + j], s = sin_t[(size_t)pos * half + j];
+        T* x = row + h * dk;
+        const float a = to_f32(x[j]), b = to_f32(x[j + half]);
+        x[j] = from_f32<T>(a * c - b * s);
+        x[j + half] = from_f32<T>(b * c + a * s);
+    }
+    if (APPEND && store) {
+        __syncthreads();
+        const T* k = row + nh * dk;
+        const T* v = k + nkvh * dk;
+        for (int i = threadIdx.x; i < nkvh * dk; i += blockDim.x) {
+            const int h = i / dk, j = i - h * dk;
+            kpool[paged_row(table, ring, pos, h, nkvh, dk, pinned) + j] = k[i];
+        }
+        for (int i = threadIdx.x; i < nkvh * dv; i += blockDim.x) {
+            const int h = i / dv, j = i - h * dv;
+            vpool[paged_row(table, ring, pos, h, nkvh, dv, pinned) + j] = v[i];
+        }
+    }
+}
+
+LLB_API int llb_rope_lead_append(void* proj, int dtype, int T, int row_stride, int nh, int nkvh, int dk, int dv, int rot,
+                                 const float* cos_t, const float* sin_t, int table_rows, const int* tok_pos, int do_append,
+                                 const int* tok_seq, const int* seq_start, const int* seq_len_before, void* kpool,
+                                 void* vpool, const int* page_table, int table_stride, int ring, int pinned, int* err,
+                                 cudaStream_t stream) {
+    if (T == 0) return 0;
+    if (rot % 2 || rot > dk || rot < 0) return (int)cudaErrorInvalidValue;
+    if (rot == 0 && !do_append) return 0;
+#define LLB_RLA(A)                                                                                                     \
+    llb_launch(rope_lead_append_kernel<TT, A>, dim3(T), dim3(128), 0, stream, (TT*)proj, row_stride, nh, nkvh, dk, dv,  \
+               rot, cos_t, sin_t, table_rows, tok_pos, tok_seq, seq_start, seq_len_before, (TT*)kpool, (TT*)vpool,      \
+               page_table, table_stride, ring, pinned, err)
+    LLB_DISPATCH_DTYPE(dtype, TT, {
+        if (do_append) LLB_RLA(true);
+        else LLB_RLA(false);
+    });
+#undef LLB_RLA
+    return llb_status();
+}
+
+// ------------------------------------------------------------------ squared ReLU
+// x <- max(x, 0)^2 in place, float32 arithmetic, one rounding.
+template <typename T>
+__global__ void relu_squared_kernel(T* __restrict__ x, size_t n) {
+    llb_grid_dependency_sync();
+    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    float v = fmaxf(to_f32(x[i]), 0.f);
+    x[i] = from_f32<T>(v * v);
+}
+
+LLB_API int llb_relu_squared(void* x, int dtype, long long n, cudaStream_t stream) {
+    if (n <= 0) return 0;
+    LLB_DISPATCH_DTYPE(dtype, TT,
+        llb_launch(relu_squared_kernel<TT>, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, stream, (TT*)x, (size_t)n));
+    return llb_status();
+}
+
 // ------------------------------------------------------------------ misc
 LLB_API const char* llb_error_string(int code) { return cudaGetErrorString((cudaError_t)code); }

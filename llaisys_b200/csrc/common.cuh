@@ -76,12 +76,22 @@ __device__ __forceinline__ float warp_max(float v) {
 // One layer's keys or values live in pages of LLB_PAGE tokens: pool[page][kv_head][token][dim].
 // A sequence's page table lists its physical pages; logical page lp sits at entry lp % ring
 // (ring is the table length for layers that keep every key, and the ring length for layers
-// that keep a window).
+// that keep a window).  A layer that also keeps its first tokens for good has `pinned` pages
+// ahead of the ring: logical page lp < pinned sits at entry lp, any later one at entry
+// pinned + (lp - pinned) % ring.
+__device__ __forceinline__ int paged_entry(int lp, int ring, int pinned) {
+    return lp < pinned ? lp : pinned + (lp - pinned) % ring;
+}
 __device__ __forceinline__ size_t paged_row(const int* table, int ring, int pos, int kvh,
-                                            int n_kv_heads, int head_dim) {
+                                            int n_kv_heads, int head_dim, int pinned = 0) {
     int lp = pos / LLB_PAGE;
-    int page = table[lp % ring];
+    int page = table[paged_entry(lp, ring, pinned)];
     return (((size_t)page * n_kv_heads + kvh) * LLB_PAGE + (pos % LLB_PAGE)) * (size_t)head_dim;
+}
+// A token at logical page lp of a step whose last token lies in logical page last_lp is stored unless a later
+// token of the same step would overwrite its ring entry.
+__device__ __forceinline__ bool paged_survives(int lp, int last_lp, int ring, int pinned) {
+    return lp < pinned || lp + ring > last_lp;
 }
 
 static inline int llb_status() { return (int)cudaGetLastError(); }

@@ -90,6 +90,10 @@ class StepContext:
     def kv(self, call: int) -> KVView:
         return self.cache.view(call, self._tables)
 
+    def token_state(self) -> torch.Tensor:
+        """int32 [n_slots, k] that the embedding part carries from step to step; row seq_slot[b] belongs to sequence b."""
+        return self.cache.token_state
+
     def state(self, call: int) -> torch.Tensor:
         """float32 [n_slots, state_size] of this call; row seq_slot[b] belongs to sequence b."""
         return self.cache.state[call]

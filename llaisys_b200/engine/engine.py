@@ -58,7 +58,7 @@ class Engine:
         self.model, self.spec, self.env = model, model.spec, model.env
         _require_cuda(self.env.device)
         self.cache = PagedCache(model.kv_needs(), model.cache_of(), model.state_sizes(), cache_config,
-                                self.env.dtype, self.env.device)
+                                self.env.dtype, self.env.device, token_state=model.token_state_ints())
         self.sm_count = torch.cuda.get_device_properties(self.env.device).multi_processor_count
         self.err = torch.zeros(1, dtype=torch.int32, device=self.env.device)
         # with kernel timers on, steps run uncaptured: a replayed graph has no launches to put events around
@@ -278,7 +278,7 @@ class Engine:
             ring, seen = self.cache.rings[g], set()
             for b in range(B):
                 used = self.cache.book.pages_needed(g, int(lens[b]) + ctx.n_new[b])
-                if used > w or (ring is not None and used > ring):
+                if used > w or (ring is not None and used > ring + self.cache.pinned[g]):
                     wrong.append(f"sequence {b} needs {used} pages of group {g}; its table row has {w}, its ring {ring}")
                     continue
                 for pg in table[b, :used].tolist():

@@ -62,6 +62,11 @@ class DecoderModel:
             out.append(theirs[k])
         return out
 
+    def token_state_ints(self) -> int:
+        """int32 values per cache slot that the embedding part carries from step to step (e.g. a sequence's last token)."""
+        f = getattr(self.embedding, "token_state_ints", None)
+        return int(f()) if f else 0
+
     def state_sizes(self) -> List[int]:
         return [self._mixer(u).state_size() for u in range(len(self.users))]
 

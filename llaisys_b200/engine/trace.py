@@ -55,7 +55,7 @@ def main(argv=None) -> int:
     ap.add_argument("--dtype", required=True, choices=sorted(DTYPES))
     ap.add_argument("--out", required=True, help="folder the logits files are written to")
     ap.add_argument("--max-tokens", type=int, required=True,
-                    help="most tokens live requests hold at any time, each rounded up to a multiple of 64")
+                    help="most tokens live requests hold at any time")
     ap.add_argument("--device", default="cuda:0")
     args = ap.parse_args(argv)
 
@@ -67,8 +67,11 @@ def main(argv=None) -> int:
     out_dir = Path(args.out)
     out_dir.mkdir(parents=True, exist_ok=True)
     cfg = load_config(args.model)
+    # --max-tokens counts tokens; the cache counts whole pages per request, so every live request may hold one
+    # partly filled page more than its tokens need: room for 256 of those
+    from ..cache.kv import PAGE
     engine = build_engine(cfg.to_spec(), DTYPES[args.dtype], args.device,
-                          CacheConfig(max_tokens=args.max_tokens), FolderSource(args.model))
+                          CacheConfig(max_tokens=args.max_tokens + 256 * PAGE), FolderSource(args.model))
 
     def emit(s):
         sys.stdout.write(s + "\n")

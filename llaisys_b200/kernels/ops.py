@@ -3,6 +3,7 @@ from __future__ import annotations
 import ctypes
 import functools
 from ctypes import c_double, c_float, c_int, c_longlong, c_ulonglong, c_void_p
+from dataclasses import dataclass
 from typing import Optional
 
 import torch
@@ -125,6 +126,78 @@ def embedding(ids: torch.Tensor, table: torch.Tensor, err: torch.Tensor) -> torc
     f = _fn(_lib_basic(), "llb_embedding", [c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p])
     _check(f(_ptr(out), _ptr(table), _dt(table), _ptr(ids), T, H, V, _ptr(err), _stream()), "embedding")
     return out
+
+
+def embedding_pair(ctx, table: torch.Tensor, scale: float, pair_table: Optional[torch.Tensor] = None, buckets: int = 0,
+                   mul_prev: int = 0, mul_cur: int = 0, last: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """float32 [T, H]: table[id] * scale, plus (with pair_table [buckets + 1, H]) the row that the hash
+    (previous id * mul_prev + id * mul_cur) mod buckets of a token and the one before it in its sequence names; a
+    sequence's first token takes row `buckets`.  `last` (int32 [slots, 2]: token, position) carries every sequence's
+    last token from step to step; the kernel reads and rewrites the rows of the step's sequences.  err 1: an id
+    outside the table; err 3: `last` does not hold the token just before the step's first."""
+    ids = ctx.tokens
+    _need_cuda(ids, table, pair_table, last)
+    T, (V, H) = ids.numel(), table.shape
+    if pair_table is not None:
+        assert pair_table.dtype == table.dtype and pair_table.shape == (buckets + 1, H) and last is not None
+        assert last.dtype == torch.int32 and last.is_contiguous() and last.shape[1] == 2
+    out = torch.empty((T, H), dtype=torch.float32, device=table.device)
+    f = _fn(_lib_basic(), "llb_embedding_pair",
+            [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
+             c_int, c_float, c_longlong, c_longlong, c_longlong, c_void_p, c_void_p])
+    _check(f(_ptr(out), _ptr(table), _ptr(pair_table), _dt(table), _ptr(ids), _ptr(ctx.tok_pos), _ptr(ctx.tok_seq),
+             _ptr(ctx.seq_start), _ptr(ctx.seq_slot), _ptr(last), T, H, V, scale, buckets, mul_prev, mul_cur, _ptr(ctx.err),
+             _stream()), "embedding (scaled, with pair rows)")
+    return out
+
+
+def rmsnorm_multi(x: torch.Tensor, weights, eps: float, out_dtype: torch.dtype):
+    """One root mean square per row of the float32 stream x [T, H], one output per weight (one or two):
+    out_i = x / sqrt(mean(x^2) + eps) * w_i."""
+    _need_cuda(x, *weights)
+    assert x.dtype == torch.float32 and x.is_contiguous() and 1 <= len(weights) <= 2
+    assert all(w.dtype == weights[0].dtype and w.is_contiguous() for w in weights)
+    T, H = x.shape
+    outs = [torch.empty((T, H), dtype=out_dtype, device=x.device) for _ in weights]
+    f = _fn(_lib_basic(), "llb_rmsnorm_multi", [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int,
+                                                c_float, c_void_p])
+    _check(f(_ptr(x), _ptr(weights[0]), _ptr(weights[1]) if len(weights) > 1 else None, _dt(weights[0]), _ptr(outs[0]),
+             _ptr(outs[1]) if len(outs) > 1 else None, DT[out_dtype], T, H, eps, _stream()), "rmsnorm (shared root mean square)")
+    return outs
+
+
+def relu_squared_(x: torch.Tensor) -> torch.Tensor:
+    """x <- max(x, 0)^2 in place (contiguous)."""
+    _need_cuda(x)
+    assert x.is_contiguous()
+    f = _fn(_lib_basic(), "llb_relu_squared", [c_void_p, c_int, c_longlong, c_void_p])
+    _check(f(_ptr(x), _dt(x), x.numel(), _stream()), "relu squared")
+    return x
+
+
+def rope_lead_append(proj: torch.Tensor, nh: int, nkvh: int, dk: int, dv: int, rot: int, *, cos=None, sin=None, tok_pos=None,
+                     append=None, err=None):
+    """In place on packed projections [T, nh dk (+ nkvh dk + nkvh dv)]: rotate the first `rot` dimensions of the query
+    heads and of the nkvh key heads (pairs (j, j + rot/2), tables [rows, rot/2]) and, with `append`, write keys and
+    values to the paged cache.  nkvh 0: the rows hold queries only.
+    append = dict(tok_seq, seq_start, seq_len_before, kpool, vpool, page_table, ring, pinned)."""
+    _need_cuda(proj, tok_pos)
+    T = proj.shape[0]
+    assert proj.stride(1) == 1
+    if tok_pos is None or tok_pos.numel() != T or err is None:
+        raise KernelError("rope_lead_append needs tok_pos (one position per packed token) and an error word")
+    if cos is None:
+        rot = 0
+    a = append or {}
+    pt = a.get("page_table")
+    f = _fn(_lib_basic(), "llb_rope_lead_append",
+            [c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p, c_int,
+             c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p])
+    _check(f(_ptr(proj), _dt(proj), T, proj.stride(0), nh, nkvh, dk, dv, rot, _ptr(cos), _ptr(sin),
+             cos.shape[0] if cos is not None else 0, _ptr(tok_pos), int(append is not None), _ptr(a.get("tok_seq")),
+             _ptr(a.get("seq_start")), _ptr(a.get("seq_len_before")), _ptr(a.get("kpool")), _ptr(a.get("vpool")), _ptr(pt),
+             pt.shape[1] if pt is not None else 0, a.get("ring", 1), a.get("pinned", 0), _ptr(err), _stream()),
+           "rotation of leading dimensions / cache append")
 
 
 def gather_i32(dst: torch.Tensor, src: torch.Tensor, idx: torch.Tensor):
@@ -507,7 +580,8 @@ class _AttnParams(ctypes.Structure):
                 ("out", c_void_p), ("kpool", c_void_p), ("vpool", c_void_p), ("page_table", c_void_p),
                 ("table_stride", c_int), ("ring", c_int), ("seq_start", c_void_p),
                 ("seq_len_before", c_void_p), ("nh", c_int), ("nkvh", c_int), ("window", c_int),
-                ("scale", c_float), ("all_from_cache", c_int), ("n_splits", c_int), ("part_o", c_void_p), ("part_ml", c_void_p)]
+                ("scale", c_float), ("all_from_cache", c_int), ("n_splits", c_int), ("part_o", c_void_p), ("part_ml", c_void_p),
+                ("keep_first", c_int), ("pinned", c_int), ("sink", c_int)]
 
 
 class _MmaAttnParams(ctypes.Structure):
@@ -576,18 +650,37 @@ def _mma_lib(dh: int):
     return lib
 
 
-def _attn_lib(dh: int):
+def _attn_lib(dh: int, dv: Optional[int] = None):
     require_head_dim(dh)
-    return load_module("attention_simt.cu", {"LLB_HEAD_DIM": dh})
+    if dv is None or dv == dh:
+        return load_module("attention_simt.cu", {"LLB_HEAD_DIM": dh})
+    require_head_dim(dv)
+    return load_module("attention_simt.cu", {"LLB_HEAD_DIM": dh, "LLB_VALUE_DIM": dv})
+
+
+@dataclass(frozen=True)
+class AttnExtras:
+    """What the plain causal (windowed) softmax attention does not have: values of a width of their own, first keys
+    that stay visible behind a window (`keep_first`, held in `pinned` pages ahead of the cache ring), and a
+    value-less sink term of score 0 in the softmax's denominator."""
+    value_dim: Optional[int] = None
+    keep_first: int = 0
+    pinned: int = 0
+    sink: bool = False
+
+    def plain(self, dh: int) -> bool:
+        return self.value_dim in (None, dh) and not self.keep_first and not self.pinned and not self.sink
 
 
 def _attn_params(qkv, out, nh, nkvh, dh, kpool, vpool, page_table, ring, seq_start, seq_len_before,
-                 window, scale, cls=None):
+                 window, scale, cls=None, extras: Optional[AttnExtras] = None):
     es = qkv.element_size()
     p = (cls or _AttnParams)()
     p.q = qkv.data_ptr()
     p.k_new = qkv.data_ptr() + nh * dh * es
     p.v_new = qkv.data_ptr() + (nh + nkvh) * dh * es
+    if extras is not None and cls is None:
+        p.keep_first, p.pinned, p.sink = (extras.keep_first if window else 0), extras.pinned, int(extras.sink)
     p.row_stride = qkv.stride(0)
     p.out = out.data_ptr()
     p.kpool, p.vpool = kpool.data_ptr(), vpool.data_ptr()
@@ -600,7 +693,7 @@ def _attn_params(qkv, out, nh, nkvh, dh, kpool, vpool, page_table, ring, seq_sta
 
 def attention_prefill(qkv, nh, nkvh, dh, kpool, vpool, page_table, ring, seq_start, seq_len_before,
                       n_seqs: int, max_new: int, window, scale, all_from_cache: bool = False,
-                      tc_split: int = 0) -> torch.Tensor:
+                      tc_split: int = 0, extras: Optional[AttnExtras] = None) -> torch.Tensor:
     """Attention of the new tokens of each sequence over its cached keys (positions before the
     step) and the step's own keys, read from the packed projections `qkv` [T, (nh + 2 nkvh) dh]
     whose query and key heads are already rotated.  With all_from_cache the step's keys are
@@ -608,6 +701,9 @@ def attention_prefill(qkv, nh, nkvh, dh, kpool, vpool, page_table, ring, seq_sta
     tc_split: CTAs per row block of the tcgen05 kernel (1, 2 or 4; 0: chosen by the number of row blocks)."""
     _need_cuda(qkv, kpool, vpool, page_table)
     assert qkv.dtype == kpool.dtype == vpool.dtype
+    if extras is not None and not extras.plain(dh):
+        return _attention_extras(False, qkv, nh, nkvh, dh, kpool, vpool, page_table, ring, seq_start, seq_len_before,
+                                 n_seqs, max_new, window, scale, all_from_cache, 1, extras)
     out = torch.empty((qkv.shape[0], nh * dh), dtype=qkv.dtype, device=qkv.device)
     if all_from_cache and prefill_tc_ok(qkv.dtype, dh) and ring >= page_table.shape[1] and qkv.stride(0) % 8 == 0:
         p = _TcAttnParams()
@@ -640,7 +736,8 @@ def attention_prefill(qkv, nh, nkvh, dh, kpool, vpool, page_table, ring, seq_sta
 
 
 def attention_decode(qkv, nh, nkvh, dh, kpool, vpool, page_table, ring, seq_start, seq_len_before,
-                     n_seqs: int, window, scale, n_splits: int = 1, rope=None, append_new: bool = False) -> torch.Tensor:
+                     n_seqs: int, window, scale, n_splits: int = 1, rope=None, append_new: bool = False,
+                     extras: Optional[AttnExtras] = None) -> torch.Tensor:
     """Attention of one new token per sequence over the cache.
 
     By default the new token's (rotated) key and value are already in the cache.  Where
@@ -649,6 +746,11 @@ def attention_decode(qkv, nh, nkvh, dh, kpool, vpool, page_table, ring, seq_star
     `qkv`, use them and write them to the cache."""
     _need_cuda(qkv, kpool, vpool, page_table)
     assert qkv.dtype == kpool.dtype == vpool.dtype
+    if extras is not None and not extras.plain(dh):
+        if rope is not None or append_new:
+            raise KernelError("attention_decode: the fused rotation / append is not available with these options")
+        return _attention_extras(True, qkv, nh, nkvh, dh, kpool, vpool, page_table, ring, seq_start, seq_len_before,
+                                 n_seqs, 1, window, scale, True, n_splits, extras)
     out = torch.empty((qkv.shape[0], nh * dh), dtype=qkv.dtype, device=qkv.device)
     mma = _mma_ok(qkv, dh)
     p = _attn_params(qkv, out, nh, nkvh, dh, kpool, vpool, page_table, ring, seq_start, seq_len_before, window, scale,
@@ -677,6 +779,114 @@ def attention_decode(qkv, nh, nkvh, dh, kpool, vpool, page_table, ring, seq_star
         _check(f(p, _dt(qkv), n_seqs, _stream()), "attention_decode", 2 if n_splits > 1 else 1)
     del keep
     return out
+
+
+def _attention_extras(decode, qkv, nh, nkvh, dh, kpool, vpool, page_table, ring, seq_start, seq_len_before, n_seqs,
+                      max_new, window, scale, all_from_cache, n_splits, extras: AttnExtras) -> torch.Tensor:
+    """Attention with AttnExtras.  qkv holds nh query heads of dh, then (unless everything comes from the cache) nkvh key
+    heads of dh and nkvh value heads of value_dim."""
+    dv = extras.value_dim or dh
+    out = torch.empty((qkv.shape[0], nh * dv), dtype=qkv.dtype, device=qkv.device)
+    p = _attn_params(qkv, out, nh, nkvh, dh, kpool, vpool, page_table, ring, seq_start, seq_len_before, window, scale,
+                     extras=extras)
+    p.v_new = qkv.data_ptr() + (nh + nkvh) * dh * qkv.element_size()
+    p.all_from_cache = int(all_from_cache)
+    lib = _attn_lib(dh, dv)
+    if not decode:
+        f = _fn(lib, "llb_attn_prefill", [_AttnParams, c_int, c_int, c_int, c_void_p])
+        _check(f(p, _dt(qkv), n_seqs, max_new, _stream()), "attention_prefill")
+        return out
+    keep = None
+    p.n_splits = n_splits
+    if n_splits > 1:
+        part_o = torch.empty((n_seqs, nh, n_splits, dv), dtype=torch.float32, device=qkv.device)
+        part_ml = torch.empty((n_seqs, nh, n_splits, 2), dtype=torch.float32, device=qkv.device)
+        p.part_o, p.part_ml = part_o.data_ptr(), part_ml.data_ptr()
+        keep = (part_o, part_ml)
+    f = _fn(lib, "llb_attn_decode", [_AttnParams, c_int, c_int, c_void_p])
+    _check(f(p, _dt(qkv), n_seqs, _stream()), "attention_decode", 2 if n_splits > 1 else 1)
+    del keep
+    return out
+
+
+# ------------------------------------------------------------------ routed experts
+def _moe_lib():
+    return load_module("moe.cu")
+
+
+_moe_tile = None
+
+
+def moe_tile_rows() -> int:
+    global _moe_tile
+    if _moe_tile is None:
+        f = _moe_lib().llb_moe_tile_rows
+        f.argtypes, f.restype = [], c_int
+        _moe_tile = int(f())
+    return _moe_tile
+
+
+def moe_route(x: torch.Tensor, router: torch.Tensor, bias: Optional[torch.Tensor], top: int, route_scale: float):
+    """(int32 [T, top] experts, float32 [T, top] weights): gates sigmoid(x router^T) in float32; the `top` largest of
+    gate + bias are chosen (first maximum first); a weight is gate * route_scale."""
+    _need_cuda(x, router, bias)
+    T, H = x.shape
+    E = router.shape[0]
+    assert router.shape == (E, H) and router.is_contiguous() and x.stride(1) == 1
+    assert bias is None or (bias.dtype == torch.float32 and bias.numel() == E)
+    idx = torch.empty((T, top), dtype=torch.int32, device=x.device)
+    wgt = torch.empty((T, top), dtype=torch.float32, device=x.device)
+    f = _fn(_moe_lib(), "llb_moe_route", [c_void_p, c_int, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_float,
+                                          c_void_p, c_void_p, c_void_p])
+    _check(f(_ptr(x), _dt(x), x.stride(0), _ptr(router), _dt(router), _ptr(bias), T, H, E, top, route_scale, _ptr(idx),
+             _ptr(wgt), _stream()), "router")
+    return idx, wgt
+
+
+class MoePlan:
+    """(token, choice) pairs grouped by expert; see csrc/moe.cu."""
+    __slots__ = ("slot_of", "pair_of", "tiles", "n_tiles", "max_tiles", "top", "n_pairs")
+
+
+def moe_plan(idx: torch.Tensor, n_experts: int) -> MoePlan:
+    _need_cuda(idx)
+    T, top = idx.shape
+    N = T * top
+    p = MoePlan()
+    p.top, p.n_pairs = top, N
+    p.max_tiles = N // moe_tile_rows() + min(n_experts, N)       # an expert that has pairs ends in one partial tile at most
+    buf = torch.empty(2 * N + 3 * p.max_tiles + 1, dtype=torch.int32, device=idx.device)
+    p.slot_of, p.pair_of = buf[:N], buf[N:2 * N]
+    p.tiles, p.n_tiles = buf[2 * N:2 * N + 3 * p.max_tiles], buf[2 * N + 3 * p.max_tiles:]
+    f = _fn(_moe_lib(), "llb_moe_plan", [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p])
+    _check(f(_ptr(idx), N, n_experts, _ptr(p.slot_of), _ptr(p.pair_of), _ptr(p.tiles), p.max_tiles, _ptr(p.n_tiles), _stream()),
+           "expert plan")
+    return p
+
+
+def moe_gemm(a: torch.Tensor, w: torch.Tensor, plan: MoePlan, gather: bool, act: Optional[str], out_dtype: torch.dtype) -> torch.Tensor:
+    """out[slot] = act(a[row(slot)] w[expert(slot)]^T) for every slot of the plan; w is [E, N, K].  gather: `a` holds the
+    tokens' rows [T, K] and a slot's row is its pair's token; else `a` is [slots, K].  act: None or "relu_squared"."""
+    _need_cuda(a, w)
+    E, N, K = w.shape
+    assert w.is_contiguous() and a.stride(1) == 1 and a.shape[1] == K
+    out = torch.empty((plan.n_pairs, N), dtype=out_dtype, device=a.device)
+    f = _fn(_moe_lib(), "llb_moe_gemm", [c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_void_p, c_int, c_void_p, c_int, c_int,
+                                         c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_void_p])
+    _check(f(_ptr(a), _dt(a), a.stride(0), _ptr(plan.pair_of), plan.top, int(gather), _ptr(w), _dt(w), _ptr(out), DT[out_dtype],
+             out.stride(0), _ptr(plan.tiles), plan.max_tiles, _ptr(plan.n_tiles), N, K, {None: 0, "relu_squared": 1}[act],
+             _stream()), "experts' product")
+    return out
+
+
+def moe_combine(stream: torch.Tensor, y: torch.Tensor, plan: MoePlan, wgt: torch.Tensor) -> None:
+    """stream[t] += sum_k wgt[t, k] * y[slot_of[t, k]] (float32 stream, k in order)."""
+    _need_cuda(stream, y, wgt)
+    T, H = stream.shape
+    assert stream.dtype == torch.float32 and stream.is_contiguous() and y.shape[1] == H and y.stride(1) == 1
+    f = _fn(_moe_lib(), "llb_moe_combine", [c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p])
+    _check(f(_ptr(stream), _ptr(y), _dt(y), y.stride(0), _ptr(plan.slot_of), _ptr(wgt), T, plan.top, H, _stream()),
+           "experts' weighted sum")
 
 
 # ------------------------------------------------------------------ choice of the next token

@@ -81,11 +81,13 @@ class TensorDecl:
 class KVNeed:
     """What a mixer keeps per token: `num_kv_heads` rows of `key_dim` elements in the key pool and
     of `value_dim` elements in the value pool (value_dim 0: no value pool, e.g. one latent row
-    per token).  `window` None keeps every token, else the last `window`."""
+    per token).  `window` None keeps every token, else the last `window` and, for good, the first
+    `keep_first` tokens of the sequence."""
     num_kv_heads: int
     key_dim: int
     value_dim: int
     window: Optional[int] = None
+    keep_first: int = 0
 
 
 class Part:

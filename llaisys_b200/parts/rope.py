@@ -64,3 +64,60 @@ class RotaryHalfSplit(PositionEncoding):
         cos, sin = self.table(ctx.max_position + 1)
         kernels.rope_append(qkv, num_heads, num_kv_heads, self.head_dim, cos=cos, sin=sin,
                             tok_pos=ctx.tok_pos, err=ctx.err)
+
+
+def _leading_tables(dims: int, base: float, device, rows: int):
+    key = ("leading", dims, base, str(device))
+    have = _TABLES.get(key)
+    if have is None or have[0].shape[0] < rows:
+        half = dims // 2
+        i = torch.arange(half, dtype=torch.float64)
+        freq = torch.pow(torch.tensor(base, dtype=torch.float64), -2.0 * i / dims)
+        ang = torch.arange(rows, dtype=torch.float64)[:, None] * freq[None, :]
+        have = (torch.cos(ang).to(torch.float32).to(device).contiguous(), torch.sin(ang).to(torch.float32).to(device).contiguous())
+        _TABLES[key] = have
+    return have
+
+
+@register_part("position", "rope_leading")
+class RotaryLeading(PositionEncoding):
+    """Rotary encoding of the first `dims` dimensions of a head: dimension i pairs with i + dims/2 (i < dims/2) and the
+    pair (a, b) at position p becomes (a cos phi - b sin phi, b cos phi + a sin phi), phi = p * base^(-2i/dims); the
+    dimensions from `dims` on pass unchanged.  dims = head_dim is the half-split rotation of whole heads; dims = 0
+    encodes nothing.  Tables [positions, dims/2] are built in float64 on the host and kept in float32, sized once by
+    prepare().  params: head_dim, dims, base."""
+    capturable = True
+
+    def __init__(self, spec, env):
+        super().__init__(spec, env)
+        self.head_dim, self.dims, self.base = int(spec.params["head_dim"]), int(spec.params["dims"]), float(spec.params["base"])
+        if self.dims % 2 or not (0 <= self.dims <= self.head_dim):
+            raise ValueError(f"rotated dimensions must be even and at most the head size {self.head_dim}, got {self.dims}")
+        self._tables = None
+        self._prepared = False
+
+    def leading_tables(self, positions: int):
+        """(cos, sin), each float32 [rows >= positions, dims / 2]; None when nothing is rotated."""
+        if self.dims == 0:
+            return None
+        if self._tables is None or self._tables[0].shape[0] < positions:
+            if self._prepared:
+                raise ValueError(f"position {positions - 1} lies beyond the {self._tables[0].shape[0]} positions the "
+                                 f"rotary table was prepared for")
+            rows = max(positions, 2 * (self._tables[0].shape[0] if self._tables is not None else 0))
+            self._tables = _leading_tables(self.dims, self.base, self.env.device, rows)
+        return self._tables
+
+    def prepare(self, max_positions):
+        self._prepared = False
+        self.leading_tables(max_positions)
+        self._prepared = True
+
+    def rotation_tables(self, positions: int):
+        return self.leading_tables(positions) if self.dims == self.head_dim else None
+
+    def apply(self, qkv, num_heads, num_kv_heads, ctx):
+        t = self.leading_tables(ctx.max_position + 1)
+        if t is not None:
+            kernels.rope_lead_append(qkv, num_heads, num_kv_heads, self.head_dim, self.head_dim, self.dims, cos=t[0], sin=t[1],
+                                     tok_pos=ctx.tok_pos, err=ctx.err)

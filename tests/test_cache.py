@@ -94,7 +94,7 @@ def _cache(needs, cache_of=None, state=None, max_tokens=640, **kw):
 def test_groups_have_storage_of_their_own():
     full, win = KVNeed(2, 16, 16, None), KVNeed(2, 16, 16, 8)
     c = _cache([full, win, win, full, KVNeed(1, 32, 32, None), None], state=[0, 0, 0, 0, 0, 12])
-    assert c.group_keys == [(2, 16, 16, None), (2, 16, 16, 2), (1, 32, 32, None)]
+    assert c.group_keys == [(2, 16, 16, None, 0), (2, 16, 16, 2, 0), (1, 32, 32, None, 0)]
     assert c.call_group == [0, 1, 1, 0, 2, None] and c.call_entry == [0, 0, 1, 1, 0, None]
     assert c.k_pools[0].shape == (2, 10, 2, 64, 16) and c.k_pools[2].shape == (1, 10, 1, 64, 32)
     assert c.state[5].shape == (10, 12)
