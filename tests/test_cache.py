@@ -103,7 +103,7 @@ def test_groups_have_storage_of_their_own():
 
 def test_keys_and_values_of_different_widths_and_a_mixer_without_values():
     c = _cache([KVNeed(2, 24, 8, None), KVNeed(1, 40, 0, None), KVNeed(2, 24, 8, None)])
-    assert c.group_keys == [(2, 24, 8, None), (1, 40, 0, None)] and c.call_entry == [0, 0, 1]
+    assert c.group_keys == [(2, 24, 8, None, 0), (1, 40, 0, None, 0)] and c.call_entry == [0, 0, 1]
     assert c.k_pools[0].shape == (2, 10, 2, 64, 24) and c.v_pools[0].shape == (2, 10, 2, 64, 8)
     assert c.k_pools[1].shape == (1, 10, 1, 64, 40) and c.v_pools[1] is None
     assert c.bytes_per_token() == 4 * (2 * 2 * (24 + 8) + 40)
