@@ -5,6 +5,9 @@ a module that is not built compiles it itself at first use."""
 TEST_MODULES = [
     *[("attention_simt.cu", {"LLB_HEAD_DIM": d}) for d in (4, 8, 10, 16, 20, 24, 32, 48, 80, 160)],
     *[("attention_mma.cu", {"LLB_HEAD_DIM": d}) for d in (16, 32, 48, 80)],
+    # keys and values of different widths, and a head size that is no multiple of 4 (test_gpu_vumezen.py)
+    *[("attention_simt.cu", {"LLB_HEAD_DIM": k, "LLB_VALUE_DIM": v}) for k, v in ((16, 24), (32, 16), (48, 32))],
+    ("attention_simt.cu", {"LLB_HEAD_DIM": 18}),
     # the build in which a bounded wait can be made to run out (test_gpu_kernels.py)
     ("gemm_tc.cu", {"LLB_WAIT_LIMIT": 4096, "LLB_TEST_STALL": 1}),
 ]
