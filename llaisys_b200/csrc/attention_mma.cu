@@ -1,7 +1,8 @@
 // bfloat16 attention over the paged cache on the tensor cores (mma.sync m16n8k16, float32
 // accumulation), for prefill and for decode.  Compiled per head size:
 // -DLLB_HEAD_DIM=<multiple of 16, at most 128>.  Same formula and masks as attention_simt.cu
-// (xsmccc/llaisys src/ops/self_attention/cpu/self_attention_cpu.cpp:28-112, plus the window).
+// (xsmccc/llaisys src/ops/self_attention/cpu/self_attention_cpu.cpp:28-112, plus the window, the first keys
+// that stay visible behind a window, and the value-less sink term of score 0 in the softmax's denominator).
 //
 // Keys and values are walked in tiles of one cache page (64 keys).  A tile's rows are fetched
 // with 16-byte cp.async copies by all threads into a ring of shared-memory stages whose rows are
@@ -71,6 +72,9 @@ struct MmaAttnParams {
     int cluster;            // the n_splits (<= 8) blocks of a (sequence, head group) are a thread-block cluster and merge
                             // their key slices through distributed shared memory; part_o / part_ml are not used
     int* err;               // decode, cluster merge: set when the bounded wait for the peers' partial sums runs out
+    int keep_first;         // with a window: keys before this position stay visible
+    int pinned;             // cache pages ahead of the ring that are never overwritten
+    int sink;               // the softmax's denominator has one more term e^0 (no value)
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -111,6 +115,11 @@ struct Source {
     const int* table;
     int ring, nkvh, kvh, row_stride, tok0, len_before;
     bool use_new;           // positions >= len_before come from k_new / v_new
+    int pinned = 0, keep = 0;
+    // a tile's first fetched key: a tile that holds kept first keys is fetched from its start
+    __device__ __forceinline__ int lo_of(int tile, int key_lo) const { return tile * TILE < keep ? tile * TILE : key_lo; }
+    // the combined walk: n_kept tiles of kept keys that lie before the window's first tile, then the window's tiles
+    __device__ __forceinline__ static int tile_at(int i, int n_kept, int tile_lo) { return i < n_kept ? i : tile_lo + i - n_kept; }
 };
 
 // Starts the copies of tile `tile` (key positions tile*TILE ...) restricted to [key_lo, key_hi] into
@@ -119,7 +128,7 @@ __device__ __forceinline__ void issue_tile(const Source& s, int tile, int key_lo
     constexpr int CH = ROW_BYTES / 16;                     // 16-byte chunks of a row
     const int p0 = tile * TILE;
     const int j_lo = max(0, key_lo - p0), j_hi = min(TILE, key_hi - p0 + 1);       // valid rows [j_lo, j_hi)
-    const size_t page_off = paged_row(s.table, s.ring, p0, s.kvh, s.nkvh, DH);      // one page per tile
+    const size_t page_off = paged_row(s.table, s.ring, p0, s.kvh, s.nkvh, DH, s.pinned);      // one page per tile
     for (int i = tid; i < TILE * CH; i += THREADS) {
         int j = i / CH, c = i - j * CH;
         if (j < j_lo || j >= j_hi) continue;
@@ -231,7 +240,7 @@ __device__ __forceinline__ void load_q(uint32_t (&qf)[KSTEPS][4], F q_of, int la
 template <int NT, bool MASKED = true>
 __device__ __forceinline__ void tile_step(const uint32_t (&qf)[KSTEPS][4], float (&o)[DTILES][4], float (&m)[2],
                                           float (&l)[2], uint32_t stage, int key0, int pos0, int lo0, int hi0, int lo1,
-                                          int hi1, float scale_log2, int lane) {
+                                          int hi1, float scale_log2, int lane, int keep = 0) {
     float s[NT][4];
 #pragma unroll
     for (int n = 0; n < NT; ++n) s[n][0] = s[n][1] = s[n][2] = s[n][3] = 0.f;
@@ -253,10 +262,10 @@ __device__ __forceinline__ void tile_step(const uint32_t (&qf)[KSTEPS][4], float
     for (int n = 0; n < NT; ++n) {
         if (MASKED) {
             int kp = pos0 + key0 + n * 8 + (lane & 3) * 2;
-            s[n][0] = (kp >= lo0 && kp <= hi0) ? s[n][0] * scale_log2 : -INFINITY;
-            s[n][1] = (kp + 1 >= lo0 && kp + 1 <= hi0) ? s[n][1] * scale_log2 : -INFINITY;
-            s[n][2] = (kp >= lo1 && kp <= hi1) ? s[n][2] * scale_log2 : -INFINITY;
-            s[n][3] = (kp + 1 >= lo1 && kp + 1 <= hi1) ? s[n][3] * scale_log2 : -INFINITY;
+            s[n][0] = ((kp >= lo0 || kp < keep) && kp <= hi0) ? s[n][0] * scale_log2 : -INFINITY;
+            s[n][1] = ((kp + 1 >= lo0 || kp + 1 < keep) && kp + 1 <= hi0) ? s[n][1] * scale_log2 : -INFINITY;
+            s[n][2] = ((kp >= lo1 || kp < keep) && kp <= hi1) ? s[n][2] * scale_log2 : -INFINITY;
+            s[n][3] = ((kp + 1 >= lo1 || kp + 1 < keep) && kp + 1 <= hi1) ? s[n][3] * scale_log2 : -INFINITY;
         } else {
             s[n][0] *= scale_log2;
             s[n][1] *= scale_log2;
@@ -428,29 +437,33 @@ __global__ void __launch_bounds__(THREADS) attn_mma_decode_kernel(MmaAttnParams 
     const int fetch_hi = p.append_new ? pos - 1 : pos;
     const float* cs = p.rope_cos ? p.rope_cos + (size_t)min(pos, p.rope_rows - 1) * (DH / 2) : nullptr;
     const float* sn = p.rope_cos ? p.rope_sin + (size_t)min(pos, p.rope_rows - 1) * (DH / 2) : nullptr;
-    int tile_lo = key_lo / TILE, tile_hi = pos / TILE + 1;
+    // the walk: the tiles of the kept first keys that lie before the window's first tile, then the window's tiles
+    const int keep = p.window > 0 ? p.keep_first : 0;
+    const int win_lo = key_lo / TILE, n_kept = min((keep + TILE - 1) / TILE, win_lo);
+    int it_lo, n_tiles;           // this block's part of the walk is [it_lo, it_lo + n_tiles)
     {   // as even a share of the tiles as there is: the slowest block of a sequence sets the time of all
-        const int n = tile_hi - tile_lo, q = n / p.n_splits, r = n - q * p.n_splits, x = blockIdx.x;
-        tile_lo += x * q + min(x, r);
-        tile_hi = tile_lo + q + (x < r ? 1 : 0);
+        const int n = n_kept + pos / TILE + 1 - win_lo, q = n / p.n_splits, r = n - q * p.n_splits, x = blockIdx.x;
+        it_lo = x * q + min(x, r);
+        n_tiles = q + (x < r ? 1 : 0);
     }
-    const int n_tiles = max(0, tile_hi - tile_lo);
+#define TILE_AT(i) Source::tile_at(it_lo + (i), n_kept, win_lo)
+    const int tile_hi = n_tiles > 0 ? TILE_AT(n_tiles - 1) + 1 : 0;          // one past the block's last tile
 
     Source src{p.kpool, p.vpool, nullptr, nullptr, p.page_table + (size_t)b * p.table_stride,
-               p.ring, p.nkvh, kvh, 0, 0, 0, false};
+               p.ring, p.nkvh, kvh, 0, 0, 0, false, p.pinned, keep};
     for (int i = 0; i < NST; ++i) {
         if (i < n_tiles)
-            issue_tile_rows(src, tile_lo + i, key_lo, fetch_hi, ring.stage(i), warp, lane,
-                            paged_row(src.table, p.ring, (tile_lo + i) * TILE, kvh, p.nkvh, DH));
+            issue_tile_rows(src, TILE_AT(i), src.lo_of(TILE_AT(i), key_lo), fetch_hi, ring.stage(i), warp, lane,
+                            paged_row(src.table, p.ring, TILE_AT(i) * TILE, kvh, p.nkvh, DH, p.pinned));
         cp_async_commit();                                 // one group per stage, empty or not
     }
     // The ring holds NST tiles; the pages of the block's next two tiles are asked into L2 now, so that their
     // copies, which can start only when a stage is free, find them there (a page is contiguous per kv head).
     // Only two: a block with a long walk (large batches) streams at full rate anyway, and asking for all its
     // pages at once was measured to cost 5 % at batch 64.
-    size_t off_ahead = NST < n_tiles ? paged_row(src.table, p.ring, (tile_lo + NST) * TILE, kvh, p.nkvh, DH) : 0;      // page of the first re-request
+    size_t off_ahead = NST < n_tiles ? paged_row(src.table, p.ring, TILE_AT(NST) * TILE, kvh, p.nkvh, DH, p.pinned) : 0;      // page of the first re-request
     for (int i = NST; i < min(n_tiles, NST + 2); ++i) {
-        const size_t off = i == NST ? off_ahead : paged_row(src.table, p.ring, (tile_lo + i) * TILE, kvh, p.nkvh, DH);
+        const size_t off = i == NST ? off_ahead : paged_row(src.table, p.ring, TILE_AT(i) * TILE, kvh, p.nkvh, DH, p.pinned);
         for (int c = tid * 64; c < TILE * DH; c += THREADS * 64) {          // 64 elements = one 128-byte line
             asm volatile("prefetch.global.L2 [%0];" ::"l"(p.kpool + off + c));
             asm volatile("prefetch.global.L2 [%0];" ::"l"(p.vpool + off + c));
@@ -504,16 +517,20 @@ __global__ void __launch_bounds__(THREADS) attn_mma_decode_kernel(MmaAttnParams 
     uint32_t qf[KSTEPS][4];
     load_q(qf, [&](int r) -> const bf16* { return qs + r * (DH + 8); }, lane);
     float o[DTILES][4], m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+    if (p.sink && blockIdx.x == 0 && warp == 0) {          // the sink's term e^0, once per query head
+        m[0] = m[1] = 0.f;
+        l[0] = l[1] = 1.f;
+    }
 #pragma unroll
     for (int d = 0; d < DTILES; ++d) o[d][0] = o[d][1] = o[d][2] = o[d][3] = 0.f;
     const float scale_log2 = p.scale * 1.4426950408889634f;
 
     for (int i = 0; i < n_tiles; ++i) {
         const size_t off_now = off_ahead;                  // page of tile i + NST, looked up a pass ago
-        if (i + 1 + NST < n_tiles) off_ahead = paged_row(src.table, p.ring, (tile_lo + i + 1 + NST) * TILE, kvh, p.nkvh, DH);
+        if (i + 1 + NST < n_tiles) off_ahead = paged_row(src.table, p.ring, TILE_AT(i + 1 + NST) * TILE, kvh, p.nkvh, DH, p.pinned);
         cp_async_wait<NST - 1>();                       // this thread's copies of tile i have landed
         __syncwarp();                                      // ... and those of the warp's other lanes: the warp's rows are there
-        if (owns_new && tile_lo + i == pos / TILE) {
+        if (owns_new && TILE_AT(i) == pos / TILE) {
             // the new token's row into this tile (and, once per kv head, into the cache).  The one place where the warps
             // meet: every warp is in this pass, so none still reads what the stage held three passes ago.
             __syncthreads();
@@ -523,17 +540,17 @@ __global__ void __launch_bounds__(THREADS) attn_mma_decode_kernel(MmaAttnParams 
                 *reinterpret_cast<uint32_t*>(krow + d * 2) = new_k;
                 *reinterpret_cast<uint32_t*>(krow + TILE_BYTES + d * 2) = new_v;
                 if (chunk == 0) {
-                    size_t goff = paged_row(src.table, p.ring, pos, kvh, p.nkvh, DH);
+                    size_t goff = paged_row(src.table, p.ring, pos, kvh, p.nkvh, DH, p.pinned);
                     *reinterpret_cast<uint32_t*>(const_cast<bf16*>(p.kpool) + goff + d) = new_k;
                     *reinterpret_cast<uint32_t*>(const_cast<bf16*>(p.vpool) + goff + d) = new_v;
                 }
             }
             __syncthreads();
         }
-        zero_unfetched_rows(ring.stage_ptr(i), tile_lo + i, key_lo, pos, warp, lane);
-        tile_step<2>(qf, o, m, l, ring.stage(i), warp * 16, (tile_lo + i) * TILE, key_lo, pos, key_lo, pos, scale_log2, lane);
+        zero_unfetched_rows(ring.stage_ptr(i), TILE_AT(i), src.lo_of(TILE_AT(i), key_lo), pos, warp, lane);
+        tile_step<2>(qf, o, m, l, ring.stage(i), warp * 16, TILE_AT(i) * TILE, key_lo, pos, key_lo, pos, scale_log2, lane, keep);
         __syncwarp();                                      // the warp's rows of the stage are free
-        if (i + NST < n_tiles) issue_tile_rows(src, tile_lo + i + NST, key_lo, fetch_hi, ring.stage(i + NST), warp, lane, off_now);
+        if (i + NST < n_tiles) issue_tile_rows(src, TILE_AT(i + NST), src.lo_of(TILE_AT(i + NST), key_lo), fetch_hi, ring.stage(i + NST), warp, lane, off_now);
         cp_async_commit();
     }
     cp_async_wait<0>();
@@ -734,12 +751,18 @@ __global__ void __launch_bounds__(THREADS, 3) attn_mma_prefill_kernel(MmaAttnPar
     const int n_rows = min(64, n_new - t0);
     const int first_pos = len_before + t0, last_pos = first_pos + n_rows - 1;
     const int key_lo = p.window > 0 ? max(0, first_pos - p.window + 1) : 0;
-    const int tile_lo = key_lo / TILE, n_tiles = last_pos / TILE + 1 - tile_lo;
+    // the walk: the tiles of the kept first keys that lie before the window's first tile, then the window's tiles
+    const int keep = p.window > 0 ? p.keep_first : 0;
+    const int tile_lo = key_lo / TILE, n_kept = min((keep + TILE - 1) / TILE, tile_lo);
+    const int n_tiles = n_kept + last_pos / TILE + 1 - tile_lo;
+#define PTILE(i) Source::tile_at(i, n_kept, tile_lo)
+    // a tile of kept keys alone is fetched, and seen by every row, up to the last kept key
+#define PTILE_HI(i) ((i) < n_kept ? keep - 1 : last_pos)
 
     Source src{p.kpool, p.vpool, p.k_new, p.v_new, p.page_table + (size_t)b * p.table_stride,
-               p.ring, p.nkvh, kvh, p.row_stride, tok0, len_before, !p.all_from_cache};
+               p.ring, p.nkvh, kvh, p.row_stride, tok0, len_before, !p.all_from_cache, p.pinned, keep};
     for (int i = 0; i < STAGES_PREFILL; ++i) {
-        if (i < n_tiles) issue_tile(src, tile_lo + i, key_lo, last_pos, ring.stage(i), tid);
+        if (i < n_tiles) issue_tile(src, PTILE(i), src.lo_of(PTILE(i), key_lo), PTILE_HI(i), ring.stage(i), tid);
         cp_async_commit();
     }
 
@@ -754,6 +777,10 @@ __global__ void __launch_bounds__(THREADS, 3) attn_mma_prefill_kernel(MmaAttnPar
     const int warp_hi = first_pos + warp * 16 + 15;                  // last position any row of this warp sees
     const int warp_lo = p.window > 0 ? max(0, first_pos + warp * 16 - p.window + 1) : 0;
     float o[DTILES][4], m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+    if (p.sink) {                                                    // the sink's term e^0
+        m[0] = m[1] = 0.f;
+        l[0] = l[1] = 1.f;
+    }
 #pragma unroll
     for (int d = 0; d < DTILES; ++d) o[d][0] = o[d][1] = o[d][2] = o[d][3] = 0.f;
     const float scale_log2 = p.scale * 1.4426950408889634f;
@@ -761,19 +788,26 @@ __global__ void __launch_bounds__(THREADS, 3) attn_mma_prefill_kernel(MmaAttnPar
     for (int i = 0; i < n_tiles; ++i) {
         cp_async_wait<STAGES_PREFILL - 1>();
         __syncthreads();
-        zero_unfetched(ring.stage_ptr(i), tile_lo + i, key_lo, last_pos, tid);
-        int p0 = (tile_lo + i) * TILE;
-        if (p0 <= warp_hi && p0 + TILE - 1 >= warp_lo) {             // the tile holds a key some row of the warp sees
+        const int tile = PTILE(i), p0 = tile * TILE;
+        zero_unfetched(ring.stage_ptr(i), tile, src.lo_of(tile, key_lo), PTILE_HI(i), tid);
+        if (i < n_kept) {
+            // kept keys that lie before every row's window: all rows see the keys below `keep` and nothing else here
+            tile_step<8, true>(qf, o, m, l, ring.stage(i), 0, p0, 0, keep - 1, 0, keep - 1, scale_log2, lane);
+        } else if (p0 <= warp_hi && (p0 + TILE - 1 >= warp_lo || p0 < keep)) {   // the tile holds a key some row of the warp sees
             // every key of the tile visible to every row of the warp (most tiles of a causal prompt): no masks
             const bool all_visible = p0 + TILE - 1 <= first_pos + warp * 16 &&
                                      (p.window <= 0 || p0 >= first_pos + warp * 16 + 15 - p.window + 1);
             if (all_visible) tile_step<8, false>(qf, o, m, l, ring.stage(i), 0, p0, lo0, hi0, lo1, hi1, scale_log2, lane);
-            else tile_step<8, true>(qf, o, m, l, ring.stage(i), 0, p0, lo0, hi0, lo1, hi1, scale_log2, lane);
+            else tile_step<8, true>(qf, o, m, l, ring.stage(i), 0, p0, lo0, hi0, lo1, hi1, scale_log2, lane, keep);
         }
         __syncthreads();
-        if (i + STAGES_PREFILL < n_tiles) issue_tile(src, tile_lo + i + STAGES_PREFILL, key_lo, last_pos, ring.stage(i + STAGES_PREFILL), tid);
+        if (i + STAGES_PREFILL < n_tiles)
+            issue_tile(src, PTILE(i + STAGES_PREFILL), src.lo_of(PTILE(i + STAGES_PREFILL), key_lo), PTILE_HI(i + STAGES_PREFILL),
+                       ring.stage(i + STAGES_PREFILL), tid);
         cp_async_commit();
     }
+#undef PTILE
+#undef PTILE_HI
     cp_async_wait<0>();
     const int c = (lane & 3) * 2;
     if (r0 < n_rows) {

@@ -591,7 +591,8 @@ class _MmaAttnParams(ctypes.Structure):
                 ("seq_len_before", c_void_p), ("nh", c_int), ("nkvh", c_int), ("window", c_int),
                 ("scale", c_float), ("all_from_cache", c_int), ("n_splits", c_int), ("part_o", c_void_p),
                 ("part_ml", c_void_p), ("rope_cos", c_void_p), ("rope_sin", c_void_p), ("rope_rows", c_int),
-                ("append_new", c_int), ("cluster", c_int), ("err", c_void_p)]
+                ("append_new", c_int), ("cluster", c_int), ("err", c_void_p),
+                ("keep_first", c_int), ("pinned", c_int), ("sink", c_int)]
 
 
 MMA_ATTENTION = True                         # tests switch the tensor-core attention off to compare
@@ -679,7 +680,7 @@ def _attn_params(qkv, out, nh, nkvh, dh, kpool, vpool, page_table, ring, seq_sta
     p.q = qkv.data_ptr()
     p.k_new = qkv.data_ptr() + nh * dh * es
     p.v_new = qkv.data_ptr() + (nh + nkvh) * dh * es
-    if extras is not None and cls is None:
+    if extras is not None:
         p.keep_first, p.pinned, p.sink = (extras.keep_first if window else 0), extras.pinned, int(extras.sink)
     p.row_stride = qkv.stride(0)
     p.out = out.data_ptr()
@@ -787,6 +788,29 @@ def _attention_extras(decode, qkv, nh, nkvh, dh, kpool, vpool, page_table, ring,
     heads of dh and nkvh value heads of value_dim."""
     dv = extras.value_dim or dh
     out = torch.empty((qkv.shape[0], nh * dv), dtype=qkv.dtype, device=qkv.device)
+    if dv == dh and _mma_ok(qkv, dh):
+        # keys and values of one width that the tensor-core kernel takes: the same kernels as the plain attention
+        p = _attn_params(qkv, out, nh, nkvh, dh, kpool, vpool, page_table, ring, seq_start, seq_len_before, window, scale,
+                         _MmaAttnParams, extras=extras)
+        p.all_from_cache = int(all_from_cache)
+        if not decode:
+            f = _fn(_mma_lib(dh), "llb_attn_mma_prefill", [_MmaAttnParams, c_int, c_int, c_void_p])
+            _check(f(p, n_seqs, max_new, _stream()), "attention_prefill (tensor cores)")
+            return out
+        n_splits = min(n_splits, 64)
+        p.cluster = int(1 < n_splits <= 8 or n_splits == 16)
+        p.err = _tc_resources(qkv.device)[2].data_ptr()
+        p.n_splits = n_splits
+        keep = None
+        if n_splits > 1 and not p.cluster:
+            part_o = torch.empty((n_seqs, nh, n_splits, dh), dtype=torch.float32, device=qkv.device)
+            part_ml = torch.empty((n_seqs, nh, n_splits, 2), dtype=torch.float32, device=qkv.device)
+            p.part_o, p.part_ml = part_o.data_ptr(), part_ml.data_ptr()
+            keep = (part_o, part_ml)
+        f = _fn(_mma_lib(dh), "llb_attn_mma_decode", [_MmaAttnParams, c_int, c_void_p])
+        _check(f(p, n_seqs, _stream()), "attention_decode (tensor cores)", 2 if (n_splits > 1 and not p.cluster) else 1)
+        del keep
+        return out
     p = _attn_params(qkv, out, nh, nkvh, dh, kpool, vpool, page_table, ring, seq_start, seq_len_before, window, scale,
                      extras=extras)
     p.v_new = qkv.data_ptr() + (nh + nkvh) * dh * qkv.element_size()
