@@ -228,6 +228,33 @@ LLB_API int llb_moe_gemm(const void* A, int a_dtype, int lda, const int* pair_of
     return llb_status();
 }
 
+// ------------------------------------------------------------------ the tokens' rows in slot order
+// out[slot, :] = x[pair_of[slot] / top, :]: the activations as the tensor-core product wants them (a tile's rows in one
+// box).  16-byte pieces where the rows allow it.
+template <typename T>
+__global__ void __launch_bounds__(256)
+moe_gather_rows_kernel(const T* __restrict__ x, int ldx, const int* __restrict__ pair_of, int top, T* __restrict__ out, int H) {
+    llb_grid_dependency_sync();
+    const int slot = blockIdx.x;
+    const T* src = x + (size_t)(pair_of[slot] / top) * ldx;
+    T* dst = out + (size_t)slot * H;
+    constexpr int V = 16 / sizeof(T);
+    if (H % V == 0 && ldx % V == 0 && !(((uintptr_t)x | (uintptr_t)out) & 15)) {
+        for (int j = threadIdx.x; j < H / V; j += blockDim.x)
+            reinterpret_cast<uint4*>(dst)[j] = reinterpret_cast<const uint4*>(src)[j];
+    } else {
+        for (int j = threadIdx.x; j < H; j += blockDim.x) dst[j] = src[j];
+    }
+}
+
+LLB_API int llb_moe_gather_rows(const void* x, int dtype, int ldx, const int* pair_of, int top, void* out, int n_slots, int H,
+                                cudaStream_t stream) {
+    if (n_slots == 0) return 0;
+    LLB_DISPATCH_DTYPE(dtype, T,
+        llb_launch(moe_gather_rows_kernel<T>, dim3(n_slots), dim3(256), 0, stream, (const T*)x, ldx, pair_of, top, (T*)out, H));
+    return llb_status();
+}
+
 // ------------------------------------------------------------------ weighted sum into the stream
 template <typename TY>
 __global__ void __launch_bounds__(256)

@@ -345,7 +345,7 @@ def _dev_key(device) -> torch.device:
 
 
 def tc_error(device, clear: bool = True) -> int:
-    """Error word of the tensor-core kernels on `device` (0: none; 101-104, 111-114, 121-122, 131-136, 141: a bounded
+    """Error word of the tensor-core kernels on `device` (0: none; 101-104, 111-114, 121-122, 131-136, 141, 151-153: a bounded
     wait ran out).  Reading it waits for the device; a code that was found is cleared, so that it is
     reported once."""
     r = _tc_res.get(_dev_key(device))
@@ -900,6 +900,48 @@ def moe_gemm(a: torch.Tensor, w: torch.Tensor, plan: MoePlan, gather: bool, act:
     _check(f(_ptr(a), _dt(a), a.stride(0), _ptr(plan.pair_of), plan.top, int(gather), _ptr(w), _dt(w), _ptr(out), DT[out_dtype],
              out.stride(0), _ptr(plan.tiles), plan.max_tiles, _ptr(plan.n_tiles), N, K, {None: 0, "relu_squared": 1}[act],
              _stream()), "experts' product")
+    return out
+
+
+def moe_tc_ok(x: torch.Tensor, up: torch.Tensor, down: torch.Tensor) -> bool:
+    """True when the experts' products of these operands run on the tensor cores (csrc/moe_tc.cu): bfloat16, both
+    reduction lengths multiples of 8, 16-byte aligned bases."""
+    return (TC_ENABLED and x.is_cuda and x.dtype == up.dtype == down.dtype == torch.bfloat16 and up.shape[2] % 8 == 0
+            and down.shape[2] % 8 == 0 and not ((up.data_ptr() | down.data_ptr()) & 15))
+
+
+def moe_gather_rows(x: torch.Tensor, plan: MoePlan) -> torch.Tensor:
+    """[slots, H]: row slot is the row of x [T, H] of the slot's token."""
+    _need_cuda(x)
+    assert x.stride(1) == 1
+    out = torch.empty((plan.n_pairs, x.shape[1]), dtype=x.dtype, device=x.device)
+    f = _fn(_moe_lib(), "llb_moe_gather_rows", [c_void_p, c_int, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_void_p])
+    _check(f(_ptr(x), _dt(x), x.stride(0), _ptr(plan.pair_of), plan.top, _ptr(out), plan.n_pairs, x.shape[1], _stream()),
+           "experts' rows in slot order")
+    return out
+
+
+def moe_gemm_tc(a: torch.Tensor, w: torch.Tensor, plan: MoePlan, epilogue: str, out: Optional[torch.Tensor] = None,
+                wgt: Optional[torch.Tensor] = None, out_dtype: torch.dtype = torch.bfloat16) -> torch.Tensor:
+    """The experts' product on tcgen05 over activations in slot order a [slots, K] (bfloat16), w [E, N, K].
+    epilogue "store" / "relu_squared": returns [slots, N] in out_dtype; "weighted_add": `out` is the float32 stream
+    [T, N] and row token(slot) gets wgt[pair(slot)] * product added (float32 atomics)."""
+    _need_cuda(a, w, out, wgt)
+    E, N, K = w.shape
+    assert w.is_contiguous() and a.stride(1) == 1 and a.shape == (plan.n_pairs, K) and a.dtype == w.dtype == torch.bfloat16
+    assert plan.max_tiles and moe_tile_rows() == 64
+    code = {"store": 0, "relu_squared": 1, "weighted_add": 2}[epilogue]
+    if code == 2:
+        assert out is not None and out.dtype == torch.float32 and out.stride(1) == 1 and out.shape[1] == N and wgt is not None
+    else:
+        out = torch.empty((plan.n_pairs, N), dtype=out_dtype, device=a.device)
+    err = _tc_resources(a.device)[2]
+    f = _fn(load_module("moe_tc.cu"), "llb_moe_gemm_tc",
+            [c_void_p, c_int, c_longlong, c_void_p, c_int, c_int, c_int, c_void_p, c_int, c_int, c_void_p, c_int, c_void_p, c_int,
+             c_void_p, c_void_p, c_int, c_void_p, c_void_p])
+    _check(f(_ptr(a), a.stride(0), plan.n_pairs, _ptr(w), E, N, K, _ptr(out), _dt(out), out.stride(0), _ptr(plan.tiles),
+             plan.max_tiles, _ptr(plan.n_tiles), code, _ptr(plan.pair_of), _ptr(wgt), plan.top, _ptr(err), _stream()),
+           "experts' product (tensor cores)")
     return out
 
 

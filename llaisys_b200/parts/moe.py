@@ -19,8 +19,10 @@ class RoutedExperts(FeedForward):
       output    sum over the chosen experts of weight * expert(h), plus shared(h)
 
     The experts' matrices are kept stacked ([E, ff, H] and [E, H, ff]).  A step's (token, choice) pairs are grouped by
-    expert on the device (kernels.moe_plan), the two products run over those groups, and the weighted sum is added to
-    the float32 residual stream in a fixed order.  Nothing is read back to the host, so a step can be captured.
+    expert on the device (kernels.moe_plan) and the two products run over those groups: in bfloat16 on tcgen05, the
+    second one ending in the weighted add into the float32 residual stream (float32 atomics, arrival order); in float32
+    (and for widths the tensor-core kernel does not take) on the CUDA cores with the weighted sum added in a fixed
+    order.  Nothing is read back to the host, so a step can be captured.
 
     params: hidden_size, experts, top, expert_ff, route_scale, act, shared_ff (None: no shared expert), use_bias, names
     (local tensor names: router, bias, expert_up, expert_down with {e} for the expert's index, shared_up, shared_down).
@@ -75,9 +77,15 @@ class RoutedExperts(FeedForward):
     def forward_into(self, x, ctx, residual):
         idx, wgt = kernels.moe_route(x, self.router, self.bias, self.top, self.route_scale)
         plan = kernels.moe_plan(idx, self.n_experts)
-        act = kernels.moe_gemm(x, self.up, plan, gather=True, act=self.act, out_dtype=x.dtype)
-        y = kernels.moe_gemm(act, self.down, plan, gather=False, act=None, out_dtype=torch.float32)
-        kernels.moe_combine(residual, y, plan, wgt)
+        if kernels.moe_tc_ok(x, self.up, self.down) and residual.stride(1) == 1:
+            # tensor cores: the tokens' rows in slot order, the up projection with its activation, and the down
+            # projection that ends in the weighted add into the stream
+            act = kernels.moe_gemm_tc(kernels.moe_gather_rows(x, plan), self.up, plan, self.act, out_dtype=x.dtype)
+            kernels.moe_gemm_tc(act, self.down, plan, "weighted_add", out=residual, wgt=wgt)
+        else:
+            act = kernels.moe_gemm(x, self.up, plan, gather=True, act=self.act, out_dtype=x.dtype)
+            y = kernels.moe_gemm(act, self.down, plan, gather=False, act=None, out_dtype=torch.float32)
+            kernels.moe_combine(residual, y, plan, wgt)
         if self.shared_ff:
             a = kernels.relu_squared_(kernels.linear(x, self.shared_up))
             if kernels.linear_into_ok(a, self.shared_down, None, residual):

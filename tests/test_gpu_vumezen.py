@@ -122,6 +122,8 @@ def test_routed_experts_alone(dtype, shape):
     part = build_part("ffn", PartSpec("routed_experts", {"hidden_size": H, "experts": E, "top": top, "expert_ff": ff, "route_scale": 1.7,
                                                          "shared_ff": 24}), BuildEnv(dtype, torch.device(DEV)))
     part.load({n: torch.from_numpy(v).to(torch.float32 if n == "correction" else dtype).to(DEV) for n, v in w.items()})
+    from llaisys_b200 import kernels
+    assert kernels.moe_tc_ok(torch.empty(1, H, dtype=dtype, device=DEV), part.up, part.down) == (dtype == torch.bfloat16)
     stream = torch.from_numpy(rng.normal(size=(T, H))).float().to(DEV)
     before = stream.clone()
     assert part.forward_into(torch.from_numpy(h).to(dtype).to(DEV), None, stream)
