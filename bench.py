@@ -482,6 +482,126 @@ REF_SOURCES = ["src/utils/*.cpp", "src/device/*.cpp", "src/device/cpu/*.cpp", "s
                "src/ops/*/*.cpp", "src/ops/*/cpu/*.cpp", "src/llaisys/*.cc", "src/models/qwen2/*.cpp"]
 
 
+# ---- `--design vumezen`: the Vumezen design beside the Qwen2 dense decoder at equal layer sizes (random weights)
+# width, heads, kv heads, head size, rotated dims, window, kept first keys, experts, top, expert ff, shared ff
+DESIGN_SIZES = {
+    "a": (1536, 12, 2, 128, 64, 1024, 4, 32, 4, 1024, 2048),
+    "b": (2048, 16, 4, 128, 64, 2048, 4, 64, 6, 1408, 2816),
+    "c": (4096, 32, 8, 128, 128, 4096, 16, 64, 8, 1536, 3072),
+}
+
+
+def design_configs(size: str, layers: int):
+    """(Vumezen config, Qwen2 config) of one size: the same width, heads and head size; the dense feed-forward as wide as
+    makes its three matrices hold what a token uses of the routed one's two (top experts and the shared one)."""
+    D, H, G, dh, rot, window, keep, E, top, ff, sff = DESIGN_SIZES[size]
+    vocab = 32768
+
+    def mixer(kv_from=None):
+        m = {"heads": H, "kv_heads": G, "dim": dh, "vdim": dh, "scale": dh ** -0.5, "rot": {"dims": rot, "base": 500000.0},
+             "mask": {"size": window, "keep_first": keep}}
+        if kv_from is not None:
+            m["kv_from"] = kv_from
+        return m
+
+    mlp = {"kind": "moe", "router": {"experts": E, "top": top, "scale": 1.5}, "expert": {"ff": ff}, "shared": {"ff": sff}}
+    vz_layers = []
+    for i in range(layers):
+        reads = i % 2 == 1                     # every second layer reads the keys and values of the layer before it
+        vz_layers.append({"type": "attention", "mixer": mixer(i - 1 if reads else None), "mlp": mlp})
+    vz = {"architecture": "Vumezen", "vocab": vocab, "width": D, "norm": {"eps": 1e-6},
+          "embedding": {"scale": 1.0, "bigram": {"buckets": 65521, "mul_prev": 31, "mul_cur": 17}}, "layers": vz_layers}
+    inter = (2 * (top * ff + sff) // 3 + 127) // 128 * 128
+    qw = dict(QWEN2_1_5B, num_hidden_layers=layers, hidden_size=D, num_attention_heads=H, num_key_value_heads=G, head_dim=dh,
+              intermediate_size=inter, vocab_size=vocab, use_sliding_window=False)
+    return vz, qw
+
+
+def design_run(args) -> int:
+    """Prefill (one step over --tokens tokens) and decode (--batch sequences that hold --tokens tokens each) of the
+    Vumezen design and of the Qwen2 dense decoder at equal layer sizes: time per step, tokens a second, and each kernel's
+    share of a step (torch.profiler).  One JSON line per model and phase.  Inputs: the weights of either model are
+    larger than L2, and nothing is flushed between steps."""
+    import collections
+    import tempfile
+
+    import numpy as np
+    import torch
+    from torch.profiler import ProfilerActivity, profile
+
+    from llaisys_b200.cache import CacheConfig
+    from llaisys_b200.config import config_from_dict
+    from llaisys_b200.engine import DecoderModel, Engine, StepEntry
+    from llaisys_b200.parts import BuildEnv
+    from llaisys_b200.weights import RandomSource, load_weights
+
+    dev = torch.device("cuda:0")
+    torch.cuda.set_device(dev)
+    layers = args.layers or 8
+    T, B = args.tokens, max(1, args.batch)
+    for size in (args.size.split(",") if args.size else sorted(DESIGN_SIZES)):
+        for name, cfg_dict in zip(("vumezen", "qwen2"), design_configs(size, layers)):
+            cfg = config_from_dict(cfg_dict)
+            model = DecoderModel(cfg.to_spec(), BuildEnv(torch.bfloat16, dev))
+            load_weights(model, RandomSource(model.expected_tensors(), seed=0, dtype=torch.bfloat16, device=dev))
+            V = model.spec.vocab_size
+            rng = np.random.default_rng(0)
+            engine = Engine(model, CacheConfig(max_tokens=(B + 1) * (T + 256), max_seqs=B + 1))
+            prompt = rng.integers(0, V, size=T).tolist()
+
+            def prefill_once():
+                s = engine.acquire()
+                engine.step([StepEntry(s, prompt, [T - 1])])
+                engine.release(s)
+
+            slots = []
+
+            def decode_once():
+                engine.step([StepEntry(s, [int(rng.integers(0, V))], [0]) for s in slots])
+
+            for phase, once, tokens in (("prefill", prefill_once, T), ("decode", decode_once, B)):
+                if phase == "decode":
+                    slots = [engine.acquire() for _ in range(B)]
+                    for s in slots:
+                        engine.step([StepEntry(s, rng.integers(0, V, size=T).tolist(), [])])
+                for _ in range(max(3, args.warmup)):
+                    once()
+                torch.cuda.synchronize()
+                steps = max(4, min(args.steps, 32))
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+                for _ in range(steps):
+                    once()
+                e1.record()
+                torch.cuda.synchronize()
+                ms = e0.elapsed_time(e1) / steps
+                with profile(activities=[ProfilerActivity.CUDA]) as prof:
+                    once()
+                    torch.cuda.synchronize()
+                with tempfile.TemporaryDirectory() as tmp:
+                    path = os.path.join(tmp, "trace.json")
+                    prof.export_chrome_trace(path)
+                    with open(path) as f:
+                        ev = [e for e in json.load(f)["traceEvents"] if e.get("cat") == "kernel"]
+                totals = collections.defaultdict(lambda: [0, 0.0])
+                for e in ev:
+                    k = e["name"].replace("(anonymous namespace)::", "").replace("void ", "").split("(")[0][:72]
+                    totals[k][0] += 1
+                    totals[k][1] += e["dur"]
+                engine.check()
+                print(json.dumps({"design": name, "size": size, "phase": phase, "layers": layers, "tokens": T, "batch": B,
+                                  "ms_per_step": round(ms, 4), "tokens_per_s": round(tokens / ms * 1e3, 1),
+                                  "weight_bytes": model.weight_bytes(),
+                                  "kernels_us": {k: [n, round(t, 1)] for k, (n, t) in sorted(totals.items(), key=lambda kv: -kv[1][1])}}),
+                      flush=True)
+            for s in slots:
+                engine.release(s)
+            del engine, model
+            gc.collect()
+            torch.cuda.empty_cache()
+    return 0
+
+
 def build_reference(src: str) -> str:
     """Copies an unmodified checkout of xsmccc/llaisys to baseline/_ref and compiles its C++ sources with g++ into
     the shared library that its Python package loads (the project builds with xmake, which is not installed; the
@@ -632,9 +752,15 @@ def main() -> int:
                          "of the prefill's products alone at --tokens tokens; builds that kernel with -DLLB_STAMPS=1")
     ap.add_argument("--timeline", choices=["decode", "prefill"], default=None,
                     help="print the per-kernel timeline of a step (torch.profiler, no ncu) instead of measuring")
+    ap.add_argument("--design", choices=["vumezen"], default=None,
+                    help="measure this design beside the Qwen2 dense decoder at equal layer sizes (prefill of --tokens tokens, "
+                         "decode at --batch) instead of the benchmark; --size picks among the sizes (default: all)")
+    ap.add_argument("--size", default=None, help="with --design: comma-separated sizes of " + ", ".join(sorted(DESIGN_SIZES)))
     args = ap.parse_args()
     if args.impl == "reference":
         return reference_arm(args)
+    if args.design:
+        return design_run(args)
     if args.stamps:
         os.environ["LLAISYS_STAMPS"] = "1"           # read when the package is imported, below
     if args.gpus != 1:

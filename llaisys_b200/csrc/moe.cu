@@ -1,11 +1,12 @@
 // Routed experts: the router, the plan that sorts (token, choice) pairs by expert, the matrix products of the
 // experts over their own tokens, and the weighted sum back into the residual stream.
 //
-//   route    z = Wr h (float32), g = 1 / (1 + e^-z); the `top` experts with the largest g + bias are chosen (ties go
-//            to the lower index); a chosen expert's weight is g * route_scale, not renormalised.
+//   select   from the router's logits z = Wr h (float32): g = 1 / (1 + e^-z); the `top` experts with the largest
+//            g + bias are chosen (ties go to the lower index); a chosen expert's weight is g * route_scale, not
+//            renormalised.
 //   plan     pair i = (token i / top, choice i % top).  Pairs are grouped by expert: slot_of[pair] is a pair's place
 //            in that order, pair_of[slot] its inverse, and every expert's run of slots is cut into tiles of
-//            MOE_TILE rows (tile -> expert, first slot, rows), so that the products below run over a grid whose size
+//            `tile_rows` rows (tile -> expert, first slot, rows), so that the products run over a grid whose size
 //            depends on the step's shape alone and never on the routing (a captured step stays valid).
 //   product  out[slot, :] = act(A[row(slot), :] W[expert(slot)]^T) on the CUDA cores, float32 accumulation (the true
 //            32-bit path, and the bfloat16 path wherever the tensor-core kernel below does not apply).
@@ -14,11 +15,13 @@
 
 constexpr int MOE_TILE = 64;
 
-// ------------------------------------------------------------------ router
-template <typename TX, typename TW>
+// ------------------------------------------------------------------ router: gates and choice from the logits
+// z [T, E] are the router's logits in float32 (a matrix product of the activations with the router's matrix, float32
+// accumulation).  A warp per token: gates g = 1 / (1 + e^-z), choice scores g + bias, the `top` largest by repeated
+// arg-max (ties to the lower index), weights g * route_scale.
 __global__ void __launch_bounds__(128)
-moe_route_kernel(const TX* __restrict__ x, int ldx, const TW* __restrict__ wr, const float* __restrict__ bias, int T, int H,
-                 int E, int top, float route_scale, int* __restrict__ idx, float* __restrict__ wgt) {
+moe_select_kernel(const float* __restrict__ z, int ldz, const float* __restrict__ bias, int T, int E, int top, float route_scale,
+                  int* __restrict__ idx, float* __restrict__ wgt) {
     extern __shared__ float sm[];                 // per warp: gate[E], choice[E]
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int t = blockIdx.x * 4 + warp;
@@ -26,17 +29,10 @@ moe_route_kernel(const TX* __restrict__ x, int ldx, const TW* __restrict__ wr, c
     float* choice = gate + E;
     llb_grid_dependency_sync();
     if (t >= T) return;
-    const TX* row = x + (size_t)t * ldx;
-    for (int e = 0; e < E; ++e) {
-        const TW* w = wr + (size_t)e * H;
-        float acc = 0.f;
-        for (int k = lane; k < H; k += 32) acc = fmaf(to_f32(row[k]), to_f32(w[k]), acc);
-        acc = warp_sum(acc);
-        if (lane == 0) {
-            const float g = 1.0f / (1.0f + expf(-acc));
-            gate[e] = g;
-            choice[e] = g + (bias ? bias[e] : 0.f);
-        }
+    for (int e = lane; e < E; e += 32) {
+        const float g = 1.0f / (1.0f + expf(-z[(size_t)t * ldz + e]));
+        gate[e] = g;
+        choice[e] = g + (bias ? bias[e] : 0.f);
     }
     __syncwarp();
     for (int k = 0; k < top; ++k) {
@@ -52,7 +48,10 @@ moe_route_kernel(const TX* __restrict__ x, int ldx, const TW* __restrict__ wr, c
             const int oa = __shfl_xor_sync(0xffffffffu, arg, o);
             if (ob > best || (ob == best && oa < arg)) { best = ob; arg = oa; }
         }
-        if (arg == 0x7fffffff) arg = 0;                    // (every score NaN: still a valid index)
+        if (arg == 0x7fffffff) {                           // every score left is NaN or -inf: the lowest index not taken yet
+            arg = 0;
+            while (arg < E - 1 && choice[arg] == -INFINITY) ++arg;
+        }
         if (lane == 0) {
             idx[(size_t)t * top + k] = arg;
             wgt[(size_t)t * top + k] = gate[arg] * route_scale;
@@ -62,25 +61,20 @@ moe_route_kernel(const TX* __restrict__ x, int ldx, const TW* __restrict__ wr, c
     }
 }
 
-LLB_API int llb_moe_route(const void* x, int x_dtype, int ldx, const void* wr, int w_dtype, const float* bias, int T, int H,
-                          int E, int top, float route_scale, int* idx, float* wgt, cudaStream_t stream) {
+LLB_API int llb_moe_select(const float* z, int ldz, const float* bias, int T, int E, int top, float route_scale, int* idx,
+                           float* wgt, cudaStream_t stream) {
     if (T == 0) return 0;
     if (top < 1 || top > E) return (int)cudaErrorInvalidValue;
     const size_t smem = (size_t)4 * 2 * E * sizeof(float);
     if (smem > 48 * 1024) return (int)cudaErrorInvalidValue;
-    LLB_DISPATCH_DTYPE(x_dtype, TX, {
-        LLB_DISPATCH_DTYPE(w_dtype, TW, {
-            llb_launch(moe_route_kernel<TX, TW>, dim3((T + 3) / 4), dim3(128), smem, stream, (const TX*)x, ldx, (const TW*)wr,
-                       bias, T, H, E, top, route_scale, idx, wgt);
-        });
-    });
+    llb_launch(moe_select_kernel, dim3((T + 3) / 4), dim3(128), smem, stream, z, ldz, bias, T, E, top, route_scale, idx, wgt);
     return llb_status();
 }
 
 // ------------------------------------------------------------------ plan
-// One block.  tiles: int32 [3, max_tiles] (expert, first slot, rows) and n_tiles [1]; max_tiles >= N / MOE_TILE + min(E, N).
+// One block.  tiles: int32 [3, max_tiles] (expert, first slot, rows) and n_tiles [1]; max_tiles >= N / tile_rows + min(E, N).
 __global__ void __launch_bounds__(1024)
-moe_plan_kernel(const int* __restrict__ idx, int N, int E, int* __restrict__ slot_of, int* __restrict__ pair_of,
+moe_plan_kernel(const int* __restrict__ idx, int N, int E, int tile_rows, int* __restrict__ slot_of, int* __restrict__ pair_of,
                 int* __restrict__ tiles, int max_tiles, int* __restrict__ n_tiles) {
     extern __shared__ int si[];                   // count[E], first[E], cursor[E], tile0[E + 1]
     int* count = si;
@@ -102,17 +96,17 @@ moe_plan_kernel(const int* __restrict__ idx, int N, int E, int* __restrict__ slo
             first[e] = f;
             tile0[e] = tl;
             f += count[e];
-            tl += (count[e] + MOE_TILE - 1) / MOE_TILE;
+            tl += (count[e] + tile_rows - 1) / tile_rows;
         }
         tile0[E] = tl;
         *n_tiles = min(tl, max_tiles);
     }
     __syncthreads();
     for (int e = tid; e < E; e += blockDim.x) {
-        for (int i = tile0[e], r = 0; i < tile0[e + 1] && i < max_tiles; ++i, r += MOE_TILE) {
+        for (int i = tile0[e], r = 0; i < tile0[e + 1] && i < max_tiles; ++i, r += tile_rows) {
             tiles[i] = e;
             tiles[max_tiles + i] = first[e] + r;
-            tiles[2 * max_tiles + i] = min(MOE_TILE, count[e] - r);
+            tiles[2 * max_tiles + i] = min(tile_rows, count[e] - r);
         }
     }
     for (int i = tid; i < N; i += blockDim.x) {
@@ -124,15 +118,16 @@ moe_plan_kernel(const int* __restrict__ idx, int N, int E, int* __restrict__ slo
     }
 }
 
-LLB_API int llb_moe_plan(const int* idx, int N, int E, int* slot_of, int* pair_of, int* tiles, int max_tiles, int* n_tiles,
-                         cudaStream_t stream) {
+LLB_API int llb_moe_plan(const int* idx, int N, int E, int tile_rows, int* slot_of, int* pair_of, int* tiles, int max_tiles,
+                         int* n_tiles, cudaStream_t stream) {
     if (N == 0) return 0;
     const size_t smem = (size_t)(4 * E + 1) * sizeof(int);
-    if (smem > 48 * 1024 || max_tiles < N / MOE_TILE + (E < N ? E : N)) return (int)cudaErrorInvalidValue;
-    llb_launch(moe_plan_kernel, dim3(1), dim3(1024), smem, stream, idx, N, E, slot_of, pair_of, tiles, max_tiles, n_tiles);
+    if (tile_rows < 1 || smem > 48 * 1024 || max_tiles < N / tile_rows + (E < N ? E : N)) return (int)cudaErrorInvalidValue;
+    llb_launch(moe_plan_kernel, dim3(1), dim3(1024), smem, stream, idx, N, E, tile_rows, slot_of, pair_of, tiles, max_tiles, n_tiles);
     return llb_status();
 }
 
+// the most rows of a tile that the CUDA-core product below takes
 LLB_API int llb_moe_tile_rows() { return MOE_TILE; }
 
 // ------------------------------------------------------------------ the experts' products on the CUDA cores

@@ -1,8 +1,9 @@
 // The experts' matrix products on the 5th-generation tensor cores (tcgen05), bfloat16 operands, float32 accumulation.
 //
-// A step's (token, choice) pairs are grouped by expert and cut into tiles of MOE_TILE slots (csrc/moe.cu, the plan).
-// A block owns one tile and 128 consecutive rows of that tile's expert matrix: the weight rows are the UMMA's M
-// operand, the tile's slots its N operand (64), both K-major, as in csrc/gemm_tc.cu.  The experts' matrices lie
+// A step's (token, choice) pairs are grouped by expert and cut into tiles of BN slots (csrc/moe.cu, the plan; BN is 16,
+// 64 or 128, chosen by how many pairs an expert gets on average).  A block owns one tile and 128 consecutive rows of
+// that tile's expert matrix: the weight rows are the UMMA's M operand, the tile's slots its N operand, both K-major,
+// as in csrc/gemm_tc.cu.  The experts' matrices lie
 // stacked as one [E * N, K] matrix, so one tensor map serves all experts and a block finds its rows at
 // expert * N + row block; the activations lie in slot order ([slots, K]: gathered rows of the step's tokens for the up
 // projection, the up projection's own output for the down projection), so a tile's operand is one box at its first
@@ -25,12 +26,14 @@
 namespace {
 
 constexpr int THREADS = 128;
-constexpr int BN = 64;                 // slots of a tile: MOE_TILE of csrc/moe.cu
-constexpr int STAGES = 4;
-constexpr int A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2, STAGE_BYTES = A_BYTES + B_BYTES;
-constexpr int BAR_OFFSET = STAGES * STAGE_BYTES;
-constexpr int SMEM_TOTAL = BAR_OFFSET + (2 * STAGES + 1) * 8 + 16 + 1024;
-constexpr int TMEM_COLS = 64;
+constexpr int A_BYTES = BM * BK * 2;
+template <int BN, int STAGES>
+struct Shape {                          // two blocks share an SM: under 113 KB each
+    static constexpr int B_BYTES = BN * BK * 2, STAGE_BYTES = A_BYTES + B_BYTES;
+    static constexpr int BAR_OFFSET = STAGES * STAGE_BYTES;
+    static constexpr int SMEM_TOTAL = BAR_OFFSET + (2 * STAGES + 1) * 8 + 16 + 1024;
+    static constexpr int TMEM_COLS = BN < 32 ? 32 : BN;
+};
 enum { ERR_MOE_WAIT_FULL = 151, ERR_MOE_WAIT_EMPTY = 152, ERR_MOE_WAIT_ACC = 153 };
 enum { EPI_STORE = 0, EPI_RELU2 = 1, EPI_WEIGHTED_ADD = 2 };
 
@@ -47,8 +50,11 @@ struct MoeTcArgs {
     int* err;
 };
 
+template <int BN, int STAGES>
 __global__ void __launch_bounds__(THREADS)
 moe_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x, MoeTcArgs g) {
+    using S = Shape<BN, STAGES>;
+    constexpr int STAGE_BYTES = S::STAGE_BYTES, BAR_OFFSET = S::BAR_OFFSET, TMEM_COLS = S::TMEM_COLS;
     extern __shared__ uint8_t smem_raw[];
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     const uint32_t bar_full = base + BAR_OFFSET, bar_empty = bar_full + 8 * STAGES, bar_acc = bar_empty + 8 * STAGES;
@@ -56,6 +62,7 @@ moe_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
     uint8_t* gen_base = smem_raw + (base - smem_u32(smem_raw));
     volatile uint32_t* tmem_slot_ptr = (volatile uint32_t*)(gen_base + BAR_OFFSET + (2 * STAGES + 1) * 8);
     __shared__ int s_abort;
+    static_assert(BN <= THREADS, "a thread per slot fills the tile's tokens and weights");
     __shared__ int s_token[BN];
     __shared__ float s_weight[BN];
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -104,7 +111,8 @@ moe_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
                     }
                     const uint32_t dst = base + s * STAGE_BYTES;
                     mbar_expect_tx(bar_full + 8 * s, STAGE_BYTES);
-                    tma_load_2d(dst, &map_w, bar_full + 8 * s, kb * BK, e * g.N + m0, HINT_EVICT_FIRST);
+                    // few slots per expert (decode): a weight tile is read once; many (prefill): the expert's next tiles read it again
+                    tma_load_2d(dst, &map_w, bar_full + 8 * s, kb * BK, e * g.N + m0, BN <= 16 ? HINT_EVICT_FIRST : HINT_EVICT_LAST);
                     tma_load_2d(dst + A_BYTES, &map_x, bar_full + 8 * s, kb * BK, slot0, HINT_EVICT_LAST);
                 }
                 if (s_abort) {
@@ -186,14 +194,30 @@ moe_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
 
 }  // namespace
 
-LLB_API int llb_moe_tc_tile_rows() { return BN; }
+template <int BN, int STAGES>
+static int launch_moe_tc(const CUtensorMap& mw, const CUtensorMap& mx, const MoeTcArgs& g, dim3 grid, cudaStream_t stream) {
+    auto k = moe_gemm_tc_kernel<BN, STAGES>;
+    constexpr int smem = Shape<BN, STAGES>::SMEM_TOTAL;
+    static bool configured[64] = {};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return (int)cudaErrorInvalidDevice;
+    if (!configured[dev]) {
+        cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        if (e != cudaSuccess) return -2000 - (int)e;
+        configured[dev] = true;
+    }
+    llb_launch(k, grid, dim3(THREADS), (size_t)smem, stream, mw, mx, g);
+    return llb_status();
+}
 
-// A [slots, K] bfloat16 (row stride lda) in slot order; W [E, N, K] bfloat16, dense.  epilogue 0: out[slots, ldo] =
-// product; 1: its squared ReLU; 2: out is the float32 stream [T, ldo] and row token(slot) gets weight(slot) * product
-// added.  K must be a multiple of 8 and all bases 16-byte aligned.
+// A [slots, K] bfloat16 (row stride lda) in slot order; W [E, N, K] bfloat16, dense; tiles of tile_rows (16, 64 or 128)
+// slots as the plan cut them.  epilogue 0: out[slots, ldo] = product; 1: its squared ReLU; 2: out is the float32 stream
+// [T, ldo] and row token(slot) gets weight(slot) * product added.  K must be a multiple of 8 and all bases 16-byte aligned.
 LLB_API int llb_moe_gemm_tc(const void* A, int lda, long long n_slots, const void* W, int E, int N, int K, void* out, int out_dtype,
-                            int ldo, const int* tiles, int max_tiles, const int* n_tiles, int epilogue, const int* pair_of,
-                            const float* wgt, int top, int* err, cudaStream_t stream) {
+                            int ldo, const int* tiles, int max_tiles, const int* n_tiles, int tile_rows, int epilogue,
+                            const int* pair_of, const float* wgt, int top, int* err, cudaStream_t stream) {
+    const int BN = tile_rows;
+    if (BN != 16 && BN != 64 && BN != 128) return (int)cudaErrorInvalidValue;
     if (max_tiles == 0 || N == 0 || n_slots == 0) return 0;
     if (K % 8 || lda % 8 || ((uintptr_t)A & 15) || ((uintptr_t)W & 15) || epilogue < 0 || epilogue > 2) return (int)cudaErrorInvalidValue;
     if (epilogue == EPI_WEIGHTED_ADD && (!pair_of || !wgt || top < 1 || out_dtype != LLB_F32)) return (int)cudaErrorInvalidValue;
@@ -205,16 +229,12 @@ LLB_API int llb_moe_gemm_tc(const void* A, int lda, long long n_slots, const voi
     if (rc) return rc;
     rc = llb_tma::bf16_map_64(A, n_slots, K, lda, BN, &mx);
     if (rc) return rc;
-    auto k = moe_gemm_tc_kernel;
-    static bool configured[64] = {};
-    int dev = 0;
-    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return (int)cudaErrorInvalidDevice;
-    if (!configured[dev]) {
-        cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_TOTAL);
-        if (e != cudaSuccess) return -2000 - (int)e;
-        configured[dev] = true;
-    }
     MoeTcArgs g{out, out_dtype, ldo, tiles, max_tiles, n_tiles, N, K, epilogue, pair_of, wgt, top, err};
-    llb_launch(k, grid, dim3(THREADS), (size_t)SMEM_TOTAL, stream, mw, mx, g);
-    return llb_status();
+    // (Measured at 2,048 tokens, 64 experts of 1,536 x 4,096, 8 per token: six stages with one block per SM instead of
+    // three with two took 441 us instead of 307; the product is bound by what 128 x 128 tiles pull from L2, not by latency.)
+    switch (BN) {
+        case 16: return launch_moe_tc<16, 5>(mw, mx, g, grid, stream);        //  91 KB
+        case 64: return launch_moe_tc<64, 4>(mw, mx, g, grid, stream);        //  97 KB
+        default: return launch_moe_tc<128, 3>(mw, mx, g, grid, stream);       //  97 KB
+    }
 }

@@ -851,40 +851,41 @@ def moe_tile_rows() -> int:
 
 
 def moe_route(x: torch.Tensor, router: torch.Tensor, bias: Optional[torch.Tensor], top: int, route_scale: float):
-    """(int32 [T, top] experts, float32 [T, top] weights): gates sigmoid(x router^T) in float32; the `top` largest of
-    gate + bias are chosen (first maximum first); a weight is gate * route_scale."""
+    """(int32 [T, top] experts, float32 [T, top] weights): the router's logits x router^T in float32 (a matrix product
+    with float32 accumulation: on the tensor cores for bfloat16 operands, on the CUDA cores in float32), gates
+    sigmoid(logits); the `top` largest of gate + bias are chosen (first maximum first); a weight is gate * route_scale."""
     _need_cuda(x, router, bias)
     T, H = x.shape
     E = router.shape[0]
     assert router.shape == (E, H) and router.is_contiguous() and x.stride(1) == 1
     assert bias is None or (bias.dtype == torch.float32 and bias.numel() == E)
+    z = linear(x, router, out_dtype=torch.float32)
     idx = torch.empty((T, top), dtype=torch.int32, device=x.device)
     wgt = torch.empty((T, top), dtype=torch.float32, device=x.device)
-    f = _fn(_moe_lib(), "llb_moe_route", [c_void_p, c_int, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_float,
-                                          c_void_p, c_void_p, c_void_p])
-    _check(f(_ptr(x), _dt(x), x.stride(0), _ptr(router), _dt(router), _ptr(bias), T, H, E, top, route_scale, _ptr(idx),
-             _ptr(wgt), _stream()), "router")
+    f = _fn(_moe_lib(), "llb_moe_select", [c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_float, c_void_p, c_void_p, c_void_p])
+    _check(f(_ptr(z), z.stride(0), _ptr(bias), T, E, top, route_scale, _ptr(idx), _ptr(wgt), _stream()), "router's choice")
     return idx, wgt
 
 
 class MoePlan:
     """(token, choice) pairs grouped by expert; see csrc/moe.cu."""
-    __slots__ = ("slot_of", "pair_of", "tiles", "n_tiles", "max_tiles", "top", "n_pairs")
+    __slots__ = ("slot_of", "pair_of", "tiles", "n_tiles", "max_tiles", "top", "n_pairs", "tile_rows")
 
 
-def moe_plan(idx: torch.Tensor, n_experts: int) -> MoePlan:
+def moe_plan(idx: torch.Tensor, n_experts: int, tile_rows: Optional[int] = None) -> MoePlan:
+    """tile_rows: slots of a tile (default: what the CUDA-core product takes, 64)."""
     _need_cuda(idx)
     T, top = idx.shape
     N = T * top
     p = MoePlan()
-    p.top, p.n_pairs = top, N
-    p.max_tiles = N // moe_tile_rows() + min(n_experts, N)       # an expert that has pairs ends in one partial tile at most
+    p.top, p.n_pairs, p.tile_rows = top, N, int(tile_rows or moe_tile_rows())
+    p.max_tiles = N // p.tile_rows + min(n_experts, N)       # an expert that has pairs ends in one partial tile at most
     buf = torch.empty(2 * N + 3 * p.max_tiles + 1, dtype=torch.int32, device=idx.device)
     p.slot_of, p.pair_of = buf[:N], buf[N:2 * N]
     p.tiles, p.n_tiles = buf[2 * N:2 * N + 3 * p.max_tiles], buf[2 * N + 3 * p.max_tiles:]
-    f = _fn(_moe_lib(), "llb_moe_plan", [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p])
-    _check(f(_ptr(idx), N, n_experts, _ptr(p.slot_of), _ptr(p.pair_of), _ptr(p.tiles), p.max_tiles, _ptr(p.n_tiles), _stream()),
-           "expert plan")
+    f = _fn(_moe_lib(), "llb_moe_plan", [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p])
+    _check(f(_ptr(idx), N, n_experts, p.tile_rows, _ptr(p.slot_of), _ptr(p.pair_of), _ptr(p.tiles), p.max_tiles, _ptr(p.n_tiles),
+             _stream()), "expert plan")
     return p
 
 
@@ -893,7 +894,7 @@ def moe_gemm(a: torch.Tensor, w: torch.Tensor, plan: MoePlan, gather: bool, act:
     tokens' rows [T, K] and a slot's row is its pair's token; else `a` is [slots, K].  act: None or "relu_squared"."""
     _need_cuda(a, w)
     E, N, K = w.shape
-    assert w.is_contiguous() and a.stride(1) == 1 and a.shape[1] == K
+    assert w.is_contiguous() and a.stride(1) == 1 and a.shape[1] == K and plan.tile_rows <= moe_tile_rows()
     out = torch.empty((plan.n_pairs, N), dtype=out_dtype, device=a.device)
     f = _fn(_moe_lib(), "llb_moe_gemm", [c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_void_p, c_int, c_void_p, c_int, c_int,
                                          c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_void_p])
@@ -908,6 +909,13 @@ def moe_tc_ok(x: torch.Tensor, up: torch.Tensor, down: torch.Tensor) -> bool:
     reduction lengths multiples of 8, 16-byte aligned bases."""
     return (TC_ENABLED and x.is_cuda and x.dtype == up.dtype == down.dtype == torch.bfloat16 and up.shape[2] % 8 == 0
             and down.shape[2] % 8 == 0 and not ((up.data_ptr() | down.data_ptr()) & 15))
+
+
+def moe_tc_tile_rows(n_pairs: int, n_experts: int) -> int:
+    """Slots of a tile of the tensor-core product: 16, 64 or 128 by the pairs an expert gets on average (a function of
+    the step's shape alone)."""
+    avg = n_pairs / max(1, n_experts)
+    return 16 if avg <= 16 else 64 if avg <= 96 else 128
 
 
 def moe_gather_rows(x: torch.Tensor, plan: MoePlan) -> torch.Tensor:
@@ -929,7 +937,7 @@ def moe_gemm_tc(a: torch.Tensor, w: torch.Tensor, plan: MoePlan, epilogue: str, 
     _need_cuda(a, w, out, wgt)
     E, N, K = w.shape
     assert w.is_contiguous() and a.stride(1) == 1 and a.shape == (plan.n_pairs, K) and a.dtype == w.dtype == torch.bfloat16
-    assert plan.max_tiles and moe_tile_rows() == 64
+    assert plan.max_tiles and plan.tile_rows in (16, 64, 128)
     code = {"store": 0, "relu_squared": 1, "weighted_add": 2}[epilogue]
     if code == 2:
         assert out is not None and out.dtype == torch.float32 and out.stride(1) == 1 and out.shape[1] == N and wgt is not None
@@ -938,9 +946,9 @@ def moe_gemm_tc(a: torch.Tensor, w: torch.Tensor, plan: MoePlan, epilogue: str, 
     err = _tc_resources(a.device)[2]
     f = _fn(load_module("moe_tc.cu"), "llb_moe_gemm_tc",
             [c_void_p, c_int, c_longlong, c_void_p, c_int, c_int, c_int, c_void_p, c_int, c_int, c_void_p, c_int, c_void_p, c_int,
-             c_void_p, c_void_p, c_int, c_void_p, c_void_p])
+             c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p])
     _check(f(_ptr(a), a.stride(0), plan.n_pairs, _ptr(w), E, N, K, _ptr(out), _dt(out), out.stride(0), _ptr(plan.tiles),
-             plan.max_tiles, _ptr(plan.n_tiles), code, _ptr(plan.pair_of), _ptr(wgt), plan.top, _ptr(err), _stream()),
+             plan.max_tiles, _ptr(plan.n_tiles), plan.tile_rows, code, _ptr(plan.pair_of), _ptr(wgt), plan.top, _ptr(err), _stream()),
            "experts' product (tensor cores)")
     return out
 

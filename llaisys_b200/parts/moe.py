@@ -76,8 +76,9 @@ class RoutedExperts(FeedForward):
 
     def forward_into(self, x, ctx, residual):
         idx, wgt = kernels.moe_route(x, self.router, self.bias, self.top, self.route_scale)
-        plan = kernels.moe_plan(idx, self.n_experts)
-        if kernels.moe_tc_ok(x, self.up, self.down) and residual.stride(1) == 1:
+        tc = kernels.moe_tc_ok(x, self.up, self.down) and residual.stride(1) == 1
+        plan = kernels.moe_plan(idx, self.n_experts, kernels.moe_tc_tile_rows(idx.numel(), self.n_experts) if tc else None)
+        if tc:
             # tensor cores: the tokens' rows in slot order, the up projection with its activation, and the down
             # projection that ends in the weighted add into the stream
             act = kernels.moe_gemm_tc(kernels.moe_gather_rows(x, plan), self.up, plan, self.act, out_dtype=x.dtype)
