@@ -1,6 +1,7 @@
 // bfloat16 prefill attention over the paged cache on the 5th-generation tensor cores (tcgen05),
 // for head sizes 64 and 128.  Same formula and masks as attention_simt.cu (xsmccc/llaisys
-// src/ops/self_attention/cpu/self_attention_cpu.cpp:28-112, plus the window).  All keys, those of
+// src/ops/self_attention/cpu/self_attention_cpu.cpp:28-112, plus the window, the first keys that stay visible
+// behind a window, and the value-less sink term e^0 in the softmax's denominator).  All keys, those of
 // the step included, are read from the cache: the caller appends before it attends.
 //
 // A CTA owns 128 consecutive new tokens of one query head.  Warps 0-3 are the softmax warps:
@@ -74,6 +75,8 @@ struct TcAttnParams {
     float scale;
     int* err;
     int n_split;                // 1, 2 or 4: CTAs (a thread-block cluster) that share the key range of a row block
+    int keep_first;             // with a window: keys before this position stay visible
+    int sink;                   // the softmax's denominator has one more term e^0 (no value)
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -253,19 +256,27 @@ attn_tc_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     const int n_rows = min(BQ, n_new - t0);
     const int first_pos = len_before + t0, last_pos = first_pos + n_rows - 1;
     const int key_lo = p.window > 0 ? max(0, first_pos - p.window + 1) : 0;
-    int tile_lo = key_lo / BKV, n_tiles = active ? last_pos / BKV + 1 - tile_lo : 0;
+    // the walk: the tiles of the kept first keys that lie before the window's first tile, then the window's tiles
+    const int keep = p.window > 0 ? p.keep_first : 0;
+    const int win_lo = key_lo / BKV, n_kept = min((keep + BKV - 1) / BKV, win_lo);
+    int it_lo = 0, n_tiles = active ? n_kept + last_pos / BKV + 1 - win_lo : 0;
     if (S > 1) {          // this CTA's even share of the row block's tiles
         const int q = n_tiles / S, r = n_tiles - q * S;
-        tile_lo += (int)rank * q + min((int)rank, r);
+        it_lo = (int)rank * q + min((int)rank, r);
         n_tiles = q + ((int)rank < r ? 1 : 0);
     }
+    auto tile_at = [&](int i) { const int it = it_lo + i; return it < n_kept ? it : win_lo + it - n_kept; };
     const int* table = p.page_table + (size_t)b * p.table_stride;
-    auto page_row = [&](int i) { return i < n_tiles ? (table[tile_lo + i] * p.nkvh + kvh) * BKV : 0; };
+    auto page_row = [&](int i) { return i < n_tiles ? (table[tile_at(i)] * p.nkvh + kvh) * BKV : 0; };
     int r0 = 0, r1 = 0, r2 = 0, r3 = 0;                             // the issuing warp: page rows of its first four tiles
     if (warp == 4) { r0 = page_row(0); r1 = page_row(1); r2 = page_row(2); r3 = page_row(3); }
     llb_grid_dependency_sync();
     bool failed = false;
     float m = -INFINITY, l = 0.f;                                   // row threads: the exponent base of the row, its sum
+    if (p.sink && rank == 0) {                                      // the sink's term e^0, once per row
+        m = 0.f;
+        l = 1.f;
+    }
     const uint32_t lane_addr = tmem + ((uint32_t)((warp & 3) * 32) << 16);
 
     if (warp == 4) {
@@ -336,7 +347,7 @@ attn_tc_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             if (!warp_wait(bar_p + 8 * s, ph, s_abort)) { failed = true; break; }
             // rows of the last page beyond the last position of this block were never written for this sequence:
             // a zero probability must meet a finite value
-            const int p0 = (tile_lo + i) * BKV;
+            const int p0 = tile_at(i) * BKV;
             if (p0 + BKV - 1 > last_pos) {
                 const int j0 = last_pos - p0 + 1;
                 for (int idx = tid - ROW_THREADS; idx < (BKV - j0) * NBLK * 8; idx += 32) {
@@ -381,7 +392,7 @@ attn_tc_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
 
         for (int i = 0; i < n_tiles && !failed; ++i) {
             const int s = i % KV_STAGES;
-            const int p0 = (tile_lo + i) * BKV;
+            const int p0 = tile_at(i) * BKV;
             if (!warp_wait(bar_s + 8 * s, (i / KV_STAGES) & 1, s_abort)) { failed = true; break; }
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             uint32_t sr[BKV];
@@ -390,10 +401,14 @@ attn_tc_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             tmem_wait();
 
             // ---- mask (only tiles that some row of the block sees in part), maximum
-            if (!(p0 + BKV - 1 <= first_pos && (p.window <= 0 || p0 >= last_pos - p.window + 1))) {
+            if (it_lo + i < n_kept) {                                // a tile of kept keys before every row's window
 #pragma unroll
                 for (int j = 0; j < BKV; ++j)
-                    if (!(p0 + j >= qlo && p0 + j <= qpos)) sr[j] = 0xff800000u;       // -inf
+                    if (p0 + j >= keep) sr[j] = 0xff800000u;                          // -inf
+            } else if (!(p0 + BKV - 1 <= first_pos && (p.window <= 0 || p0 >= last_pos - p.window + 1))) {
+#pragma unroll
+                for (int j = 0; j < BKV; ++j)
+                    if (!((p0 + j >= qlo || p0 + j < keep) && p0 + j <= qpos)) sr[j] = 0xff800000u;       // -inf
             }
             float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll

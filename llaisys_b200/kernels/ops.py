@@ -626,7 +626,7 @@ def decode_fusion_ok(dtype: torch.dtype, dh: int) -> bool:
 class _TcAttnParams(ctypes.Structure):
     _fields_ = [("out", c_void_p), ("page_table", c_void_p), ("table_stride", c_int), ("seq_start", c_void_p),
                 ("seq_len_before", c_void_p), ("nh", c_int), ("nkvh", c_int), ("window", c_int), ("scale", c_float),
-                ("err", c_void_p), ("n_split", c_int)]
+                ("err", c_void_p), ("n_split", c_int), ("keep_first", c_int), ("sink", c_int)]
 
 
 TC_ATTENTION = True                          # tests switch the tcgen05 prefill attention off to compare
@@ -707,20 +707,8 @@ def attention_prefill(qkv, nh, nkvh, dh, kpool, vpool, page_table, ring, seq_sta
                                  n_seqs, max_new, window, scale, all_from_cache, 1, extras)
     out = torch.empty((qkv.shape[0], nh * dh), dtype=qkv.dtype, device=qkv.device)
     if all_from_cache and prefill_tc_ok(qkv.dtype, dh) and ring >= page_table.shape[1] and qkv.stride(0) % 8 == 0:
-        p = _TcAttnParams()
-        p.out, p.page_table, p.table_stride = out.data_ptr(), page_table.data_ptr(), page_table.shape[1]
-        p.seq_start, p.seq_len_before = seq_start.data_ptr(), seq_len_before.data_ptr()
-        p.nh, p.nkvh, p.window, p.scale = nh, nkvh, int(window or 0), scale
-        p.err = _tc_resources(qkv.device)[2].data_ptr()
-        # few row blocks (up to one and a half per SM): two CTAs share each block's key range, so that the longest
-        # CTA gets shorter (measured at 12 heads: 30.5 vs 33.7 us at 2,048 tokens, 73 vs 64 us at 4,096; four CTAs
-        # per block always lost to the cost of the merge)
-        ctas = -(-max_new // 128) * nh * n_seqs
-        p.n_split = tc_split if tc_split else (2 if ctas * 2 <= 3 * _sm_count(qkv.device) and dh >= 64 else 1)
-        f = _fn(load_module("attention_tc.cu", {"LLB_HEAD_DIM": dh}), "llb_attn_tc_prefill",
-                [c_void_p, c_int, c_int, c_void_p, c_void_p, c_int, _TcAttnParams, c_int, c_int, c_void_p])
-        _check(f(qkv.data_ptr(), qkv.shape[0], qkv.stride(0), kpool.data_ptr(), vpool.data_ptr(), kpool.shape[0],
-                 p, n_seqs, max_new, _stream()), "attention_prefill (tcgen05)")
+        _attention_prefill_tc(qkv, out, nh, nkvh, dh, kpool, vpool, page_table, seq_start, seq_len_before, n_seqs, max_new,
+                              window, scale, tc_split)
         return out
     if _mma_ok(qkv, dh):
         p = _attn_params(qkv, out, nh, nkvh, dh, kpool, vpool, page_table, ring, seq_start, seq_len_before, window,
@@ -734,6 +722,26 @@ def attention_prefill(qkv, nh, nkvh, dh, kpool, vpool, page_table, ring, seq_sta
     f = _fn(_attn_lib(dh), "llb_attn_prefill", [_AttnParams, c_int, c_int, c_int, c_void_p])
     _check(f(p, _dt(qkv), n_seqs, max_new, _stream()), "attention_prefill")
     return out
+
+
+def _attention_prefill_tc(qkv, out, nh, nkvh, dh, kpool, vpool, page_table, seq_start, seq_len_before, n_seqs, max_new,
+                          window, scale, tc_split=0, keep_first=0, sink=False):
+    """The tcgen05 prefill kernel (csrc/attention_tc.cu): every key from a cache that keeps them all."""
+    p = _TcAttnParams()
+    p.out, p.page_table, p.table_stride = out.data_ptr(), page_table.data_ptr(), page_table.shape[1]
+    p.seq_start, p.seq_len_before = seq_start.data_ptr(), seq_len_before.data_ptr()
+    p.nh, p.nkvh, p.window, p.scale = nh, nkvh, int(window or 0), scale
+    p.keep_first, p.sink = (int(keep_first) if window else 0), int(sink)
+    p.err = _tc_resources(qkv.device)[2].data_ptr()
+    # few row blocks (up to one and a half per SM): two CTAs share each block's key range, so that the longest
+    # CTA gets shorter (measured at 12 heads: 30.5 vs 33.7 us at 2,048 tokens, 73 vs 64 us at 4,096; four CTAs
+    # per block always lost to the cost of the merge)
+    ctas = -(-max_new // 128) * nh * n_seqs
+    p.n_split = tc_split if tc_split else (2 if ctas * 2 <= 3 * _sm_count(qkv.device) and dh >= 64 else 1)
+    f = _fn(load_module("attention_tc.cu", {"LLB_HEAD_DIM": dh}), "llb_attn_tc_prefill",
+            [c_void_p, c_int, c_int, c_void_p, c_void_p, c_int, _TcAttnParams, c_int, c_int, c_void_p])
+    _check(f(qkv.data_ptr(), qkv.shape[0], qkv.stride(0), kpool.data_ptr(), vpool.data_ptr(), kpool.shape[0],
+             p, n_seqs, max_new, _stream()), "attention_prefill (tcgen05)")
 
 
 def attention_decode(qkv, nh, nkvh, dh, kpool, vpool, page_table, ring, seq_start, seq_len_before,
@@ -788,6 +796,12 @@ def _attention_extras(decode, qkv, nh, nkvh, dh, kpool, vpool, page_table, ring,
     heads of dh and nkvh value heads of value_dim."""
     dv = extras.value_dim or dh
     out = torch.empty((qkv.shape[0], nh * dv), dtype=qkv.dtype, device=qkv.device)
+    if (not decode and dv == dh and all_from_cache and prefill_tc_ok(qkv.dtype, dh) and not extras.pinned and scale > 0
+            and ring >= page_table.shape[1] and qkv.stride(0) % 8 == 0):
+        # a cache that keeps every key, head size 64 or 128: the tcgen05 prefill kernel, as for the plain attention
+        _attention_prefill_tc(qkv, out, nh, nkvh, dh, kpool, vpool, page_table, seq_start, seq_len_before, n_seqs, max_new,
+                              window, scale, 0, extras.keep_first, extras.sink)
+        return out
     if dv == dh and _mma_ok(qkv, dh):
         # keys and values of one width that the tensor-core kernel takes: the same kernels as the plain attention
         p = _attn_params(qkv, out, nh, nkvh, dh, kpool, vpool, page_table, ring, seq_start, seq_len_before, window, scale,

@@ -160,20 +160,23 @@ def test_attention_alone_at_window_and_page_edges(tmp_path, mask, shared):
     assert not engine.cache.live_slots
 
 
+@pytest.mark.parametrize("dim", [32, 64])
 @pytest.mark.parametrize("mask", MASKS)
-def test_tensor_core_attention_against_the_cuda_core_one(tmp_path, mask, monkeypatch):
-    """bfloat16, keys and values of one width: the tensor-core kernels serve the windowed sink attention.  They get the
-    same bfloat16 queries, keys and values as the CUDA-core kernel, so with sharp scores (a lost key would show) the two
+def test_tensor_core_attention_against_the_cuda_core_one(tmp_path, mask, dim, monkeypatch):
+    """bfloat16, keys and values of one width: the tensor-core kernels serve the windowed sink attention (head size 64
+    over a cache that keeps every key: the tcgen05 kernel in prompts; else the mma.sync kernels).  They get the same
+    bfloat16 queries, keys and values as the CUDA-core kernel, so with sharp scores (a lost key would show) the two
     may differ only by the rounding of the probabilities."""
     from llaisys_b200.kernels import ops
     window, keep = mask
-    cfg = vh.config(101, 32, [vh.layer(4, 2, 32, 32, 16, window, keep), vh.layer(4, 2, 32, 32, 16, max(1, window - 1), keep + 1, kv_from=0),
+    cfg = vh.config(101, 32, [vh.layer(4, 2, dim, dim, 16, window, keep), vh.layer(4, 2, dim, dim, 16, max(1, window - 1), keep + 1, kv_from=0),
                               vh.layer(3, 1, 16, 16, 16, window, keep)], scale=2.0, bigram=(17, 3, 5))
     folder = vh.make_folder(tmp_path, cfg, seed=window * 7 + keep, attn_gain=12.0)
     requests = vh.random_requests(cfg, [1, 200, 66, 131], seed=5)
     got = {}
     for mma in (True, False):
         monkeypatch.setattr(ops, "MMA_ATTENTION", mma)
+        monkeypatch.setattr(ops, "TC_ATTENTION", mma)
         engine = build_engine(folder, torch.bfloat16, max_tokens=64 * 7, max_seqs=2)
         got[mma] = [run_whole(engine, requests), run_tail_by_one(engine, requests, tail=140), run_chunked(engine, requests, [63, 2, 65, 1, 64]),
                     run_batches(engine, requests, [[1, 3], [0, 2]], [1, 100, 30, 70])]
