@@ -765,6 +765,71 @@ rope_lead_append_kernel(T* __restrict__ proj, int row_stride, int nh, int nkvh, 
     }
 }
 
+// The same for bfloat16 rows in 16-byte pieces: rot a multiple of 16, dk and dv multiples of 8, rows and pools on 16-byte
+// boundaries.  A thread rotates eight consecutive pairs at a time and copies keys and values eight elements at a time.
+template <bool APPEND>
+__global__ void __launch_bounds__(128)
+rope_lead_append_vec_kernel(bf16* __restrict__ proj, int row_stride, int nh, int nkvh, int dk, int dv, int rot,
+                            const float* __restrict__ cos_t, const float* __restrict__ sin_t, int table_rows,
+                            const int* __restrict__ tok_pos, const int* __restrict__ tok_seq,
+                            const int* __restrict__ seq_start, const int* __restrict__ seq_len_before,
+                            bf16* __restrict__ kpool, bf16* __restrict__ vpool, const int* __restrict__ page_table,
+                            int table_stride, int ring, int pinned, int* err) {
+    const int t = blockIdx.x, pos = tok_pos[t], half = rot >> 1, per_head = half >> 3;
+    bool store = false;
+    size_t k_base = 0, v_base = 0;            // element offsets of the token's row of kv head 0 in the pools
+    if (APPEND) {
+        const int s = tok_seq[t];
+        const int* table = page_table + (size_t)s * table_stride;
+        const int last = seq_len_before[s] + (seq_start[s + 1] - seq_start[s]) - 1;
+        store = paged_survives(pos / LLB_PAGE, last / LLB_PAGE, ring, pinned);
+        if (store) {
+            k_base = paged_row(table, ring, pos, 0, nkvh, dk, pinned);
+            v_base = paged_row(table, ring, pos, 0, nkvh, dv, pinned);
+        }
+    }
+    if (half > 0 && (pos < 0 || pos >= table_rows)) {
+        if (threadIdx.x == 0) atomicExch(err, 2);
+        return;
+    }
+    llb_grid_dependency_sync();
+    bf16* row = proj + (size_t)t * row_stride;
+    for (int i = threadIdx.x; i < (nh + nkvh) * per_head; i += blockDim.x) {
+        const int h = i / per_head, j = (i - h * per_head) * 8;
+        bf16* x = row + h * dk;
+        uint4 lo = *reinterpret_cast<const uint4*>(x + j), hi = *reinterpret_cast<const uint4*>(x + j + half);
+        const float4 c0 = *reinterpret_cast<const float4*>(cos_t + (size_t)pos * half + j), c1 = *reinterpret_cast<const float4*>(cos_t + (size_t)pos * half + j + 4);
+        const float4 s0 = *reinterpret_cast<const float4*>(sin_t + (size_t)pos * half + j), s1 = *reinterpret_cast<const float4*>(sin_t + (size_t)pos * half + j + 4);
+        const float c[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
+        const float sn[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
+        bf16* a = reinterpret_cast<bf16*>(&lo);
+        bf16* b = reinterpret_cast<bf16*>(&hi);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+            const float av = to_f32(a[e]), bv = to_f32(b[e]);
+            a[e] = from_f32<bf16>(av * c[e] - bv * sn[e]);
+            b[e] = from_f32<bf16>(bv * c[e] + av * sn[e]);
+        }
+        *reinterpret_cast<uint4*>(x + j) = lo;
+        *reinterpret_cast<uint4*>(x + j + half) = hi;
+    }
+    if (APPEND && store) {
+        __syncthreads();
+        const bf16* k = row + nh * dk;
+        const bf16* v = k + nkvh * dk;
+        const int kc = dk >> 3, vc = dv >> 3;
+        const size_t k_step = (size_t)LLB_PAGE * dk, v_step = (size_t)LLB_PAGE * dv;     // from one kv head's row to the next one's
+        for (int i = threadIdx.x; i < nkvh * kc; i += blockDim.x) {
+            const int h = i / kc, j = (i - h * kc) * 8;
+            *reinterpret_cast<uint4*>(kpool + k_base + h * k_step + j) = *reinterpret_cast<const uint4*>(k + h * dk + j);
+        }
+        for (int i = threadIdx.x; i < nkvh * vc; i += blockDim.x) {
+            const int h = i / vc, j = (i - h * vc) * 8;
+            *reinterpret_cast<uint4*>(vpool + v_base + h * v_step + j) = *reinterpret_cast<const uint4*>(v + h * dv + j);
+        }
+    }
+}
+
 LLB_API int llb_rope_lead_append(void* proj, int dtype, int T, int row_stride, int nh, int nkvh, int dk, int dv, int rot,
                                  const float* cos_t, const float* sin_t, int table_rows, const int* tok_pos, int do_append,
                                  const int* tok_seq, const int* seq_start, const int* seq_len_before, void* kpool,
@@ -773,6 +838,17 @@ LLB_API int llb_rope_lead_append(void* proj, int dtype, int T, int row_stride, i
     if (T == 0) return 0;
     if (rot % 2 || rot > dk || rot < 0) return (int)cudaErrorInvalidValue;
     if (rot == 0 && !do_append) return 0;
+    if (dtype == LLB_BF16 && rot % 16 == 0 && dk % 8 == 0 && dv % 8 == 0 && row_stride % 8 == 0 &&
+        !(((uintptr_t)proj | (uintptr_t)cos_t | (uintptr_t)sin_t | (uintptr_t)kpool | (uintptr_t)vpool) & 15)) {
+#define LLB_RLAV(A)                                                                                                    \
+    llb_launch(rope_lead_append_vec_kernel<A>, dim3(T), dim3(128), 0, stream, (bf16*)proj, row_stride, nh, nkvh, dk,   \
+               dv, rot, cos_t, sin_t, table_rows, tok_pos, tok_seq, seq_start, seq_len_before, (bf16*)kpool,            \
+               (bf16*)vpool, page_table, table_stride, ring, pinned, err)
+        if (do_append) LLB_RLAV(true);
+        else LLB_RLAV(false);
+#undef LLB_RLAV
+        return llb_status();
+    }
 #define LLB_RLA(A)                                                                                                     \
     llb_launch(rope_lead_append_kernel<TT, A>, dim3(T), dim3(128), 0, stream, (TT*)proj, row_stride, nh, nkvh, dk, dv,  \
                rot, cos_t, sin_t, table_rows, tok_pos, tok_seq, seq_start, seq_len_before, (TT*)kpool, (TT*)vpool,      \
