@@ -173,8 +173,8 @@ class VumezenConfig:
             shared_cache = m.kv_from is not None or bool(self.readers(i))
             mixer = PartSpec("windowed_sink_attention", {
                 "hidden_size": D, "num_heads": m.heads, "num_kv_heads": m.kv_heads, "key_dim": m.dim, "value_dim": m.vdim,
-                "scale": m.scale, "window": m.window, "keep_first": m.keep_first, "sink": True,
-                "own_kv": m.kv_from is None, "cache_window": None if shared_cache else m.window,
+                "scale": m.scale, "window": min(m.window, MAX_POSITIONS), "keep_first": min(m.keep_first, MAX_POSITIONS),
+                "sink": True, "own_kv": m.kv_from is None, "cache_window": None if shared_cache else min(m.window, MAX_POSITIONS),
                 "position": PartSpec("rope_leading", {"head_dim": m.dim, "dims": m.rot_dims, "base": m.rot_base}),
             }, prefix=f"{p}.mix")
             subs = [SubLayerSpec("mixer", mixer, PartSpec("rms_norm", norm, prefix=f"{p}.norm1"))]

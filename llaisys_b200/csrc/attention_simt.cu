@@ -1,6 +1,6 @@
 // Causal grouped-query attention over the paged cache on the CUDA cores, float32 arithmetic.
 // It serves the true 32-bit path in both phases and is the reference the tensor-core kernels
-// are checked against.  Compiled per head size: -DLLB_HEAD_DIM=<multiple of 2, at most 256>.
+// are checked against.  Compiled per head size: -DLLB_HEAD_DIM=<at most 256> (and -DLLB_VALUE_DIM for values of another width).
 //
 // Formula (src/ops/self_attention/cpu/self_attention_cpu.cpp:28-112 of xsmccc/llaisys): for a
 // query at absolute position p of head h, scores s_t = (q . k_t) * scale over the keys t of kv

@@ -638,12 +638,13 @@ def prefill_tc_ok(dtype: torch.dtype, dh: int) -> bool:
     return TC_ATTENTION and dtype == torch.bfloat16 and dh in (64, 128)
 
 
-def require_head_dim(dh: int) -> None:
+def require_head_dim(dh: int, even: bool = True) -> None:
     """Raises unless some attention kernel of this package takes heads of `dh` elements: the CUDA-core
-    kernel (both precisions) takes any even size up to 256; the tensor-core kernels take multiples of
-    16 up to 128 (mma.sync) and 64 or 128 (tcgen05) and are chosen where they apply."""
-    if dh <= 0 or dh % 2 or dh > 256:
-        raise KernelError(f"attention: head size {dh} is not supported (even, at most 256)")
+    kernel (both precisions) takes any size up to 256 (even, where whole heads are rotated in halves); the
+    tensor-core kernels take multiples of 16 up to 128 (mma.sync) and 64 or 128 (tcgen05) and are chosen
+    where they apply."""
+    if dh <= 0 or (even and dh % 2) or dh > 256:
+        raise KernelError(f"attention: head size {dh} is not supported ({'even, ' if even else ''}at most 256)")
 
 
 def _mma_lib(dh: int):
@@ -652,10 +653,10 @@ def _mma_lib(dh: int):
 
 
 def _attn_lib(dh: int, dv: Optional[int] = None):
-    require_head_dim(dh)
+    require_head_dim(dh, even=False)
     if dv is None or dv == dh:
         return load_module("attention_simt.cu", {"LLB_HEAD_DIM": dh})
-    require_head_dim(dv)
+    require_head_dim(dv, even=False)
     return load_module("attention_simt.cu", {"LLB_HEAD_DIM": dh, "LLB_VALUE_DIM": dv})
 
 

@@ -40,8 +40,8 @@ class WindowedSinkAttention(Mixer):
         self.dk, self.dv = int(p["key_dim"]), int(p["value_dim"])
         if self.nkvh <= 0 or self.nh % self.nkvh:
             raise ValueError(f"{self.nh} query heads cannot share {self.nkvh} key/value heads")
-        kernels.require_head_dim(self.dk)
-        kernels.require_head_dim(self.dv)
+        kernels.require_head_dim(self.dk, even=False)      # (the rotated part of a head is even; the head need not be)
+        kernels.require_head_dim(self.dv, even=False)
         self.scale = float(p["scale"])
         self.window = int(p["window"]) if p.get("window") is not None else None
         if self.window is not None and self.window <= 0:

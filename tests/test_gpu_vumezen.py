@@ -160,7 +160,7 @@ def test_attention_alone_at_window_and_page_edges(tmp_path, mask, shared):
     assert not engine.cache.live_slots
 
 
-@pytest.mark.parametrize("dim", [32, 64])
+@pytest.mark.parametrize("dim", [32, 64, 128])
 @pytest.mark.parametrize("mask", MASKS)
 def test_tensor_core_attention_against_the_cuda_core_one(tmp_path, mask, dim, monkeypatch):
     """bfloat16, keys and values of one width: the tensor-core kernels serve the windowed sink attention (head size 64
@@ -187,6 +187,19 @@ def test_tensor_core_attention_against_the_cuda_core_one(tmp_path, mask, dim, mo
             rms = np.sqrt((ref ** 2).mean())
             d = a[key] - ref
             assert np.sqrt((d ** 2).mean()) <= 0.015 * rms + 2e-4 and np.abs(d).max() <= 0.1 * rms + 1e-3, (mask, key)
+
+
+def test_odd_head_sizes(tmp_path):
+    """Heads of 7 with 4 rotated dimensions, values of 5: nothing in the design asks for even or aligned sizes."""
+    cfg = vh.config(53, 20, [vh.layer(3, 1, 7, 5, 4, 20, 2, moe=vh.moe(3, 2, 9, 7)), vh.layer(3, 1, 7, 5, 4, 11, 0, kv_from=0)],
+                    scale=1.3, bigram=(11, 3, 5))
+    for dtype in DTYPES:
+        c = cfg if dtype == torch.float32 else vh.variant(cfg, lambda c: c["layers"][0]["mlp"]["router"].__setitem__("top", 3))
+        folder = vh.make_folder(tmp_path / str(dtype), c, seed=4, attn_gain=vh.GAIN[dtype])
+        oracle, requests = vh.Oracle(folder), vh.random_requests(c, [1, 70, 33], seed=2)
+        engine = build_engine(folder, dtype, max_tokens=64 * 3)
+        compare(run_whole(engine, requests), oracle, requests, dtype, vh.like_config(c), "odd sizes whole")
+        compare(run_tail_by_one(engine, requests, tail=40), oracle, requests, dtype, vh.like_config(c), "odd sizes decoded")
 
 
 def test_one_far_key_that_decides(tmp_path):
