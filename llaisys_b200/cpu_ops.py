@@ -65,11 +65,42 @@ def rope(x: np.ndarray, pos_ids: np.ndarray, theta: float) -> np.ndarray:
     return np.concatenate([a * cos - b * sin, b * cos + a * sin], axis=-1)
 
 
-def self_attention(q: np.ndarray, k: np.ndarray, v: np.ndarray, scale: float, window=None) -> np.ndarray:
-    """Causal grouped-query attention of q [qlen, nh, d] over k, v [kvlen, nkvh, d], the queries being
+def rope_leading(x: np.ndarray, pos_ids: np.ndarray, dims: int, base: float) -> np.ndarray:
+    """Rotation of the first `dims` dimensions of x [seq, heads, d] in pairs (i, i + dims/2) by the angle
+    p * base^(-2i/dims); the other dimensions pass (not in xsmccc/llaisys)."""
+    x = x.astype(np.float32)
+    half = dims // 2
+    if half == 0:
+        return x
+    freq = np.power(float(base), -2.0 * np.arange(half, dtype=np.float64) / dims)
+    ang = np.asarray(pos_ids, dtype=np.float64)[:, None] * freq[None, :]
+    cos, sin = np.cos(ang)[:, None, :].astype(np.float32), np.sin(ang)[:, None, :].astype(np.float32)
+    a, b = x[..., :half], x[..., half:dims]
+    return np.concatenate([a * cos - b * sin, b * cos + a * sin, x[..., dims:]], axis=-1)
+
+
+def relu_squared(x: np.ndarray) -> np.ndarray:
+    """max(x, 0)^2 (not in xsmccc/llaisys)."""
+    r = np.maximum(x.astype(np.float32), np.float32(0))
+    return r * r
+
+
+def route_top(logits: np.ndarray, bias, top: int, scale: float):
+    """(experts [T, top], weights [T, top]) of a router: gates 1 / (1 + e^-z); the `top` largest of gate + bias, the
+    first maximum first; weights gate * scale, not renormalised (not in xsmccc/llaisys)."""
+    gate = np.float32(1.0) / (np.float32(1.0) + np.exp(-logits.astype(np.float32)))
+    choice = gate + (bias.astype(np.float32) if bias is not None else np.float32(0))
+    idx = np.argsort(-choice, axis=-1, kind="stable")[:, :top]
+    return idx, np.take_along_axis(gate, idx, axis=-1) * np.float32(scale)
+
+
+def self_attention(q: np.ndarray, k: np.ndarray, v: np.ndarray, scale: float, window=None, keep_first: int = 0,
+                   sink: bool = False) -> np.ndarray:
+    """Causal grouped-query attention of q [qlen, nh, d] over k [kvlen, nkvh, d], v [kvlen, nkvh, dv], the queries being
     the last qlen of the kvlen positions: query i sees keys t <= kvlen - qlen + i; head h reads kv head
     h // (nh / nkvh); softmax with the maximum subtracted (src/ops/self_attention/cpu/self_attention_cpu.cpp:28-112).
-    window (not in that project): a query at position p sees only the keys p - window < t <= p."""
+    Not in that project: window (a query at position p sees only the keys p - window < t <= p), keep_first (the keys
+    t < keep_first stay visible behind the window) and sink (one more term e^0 in the denominator, without a value)."""
     qlen, nh, d = q.shape
     kvlen, nkvh, dv = v.shape
     group = nh // nkvh
@@ -79,12 +110,16 @@ def self_attention(q: np.ndarray, k: np.ndarray, v: np.ndarray, scale: float, wi
     cur = (kvlen - qlen + np.arange(qlen))[:, None]
     visible = t[None, :] <= cur
     if window is not None:
-        visible &= t[None, :] > cur - window
+        visible &= (t[None, :] > cur - window) | (t[None, :] < keep_first)
     for h in range(nh):
         s = (q[:, h, :] @ k[:, h // group, :].T) * np.float32(scale)
         s = np.where(visible, s, -np.inf)
-        e = np.where(visible, np.exp(s - s.max(axis=-1, keepdims=True)), 0.0).astype(np.float32)
-        out[:, h, :] = (e / e.sum(axis=-1, keepdims=True)) @ v[:, h // group, :]
+        m = s.max(axis=-1, keepdims=True)
+        if sink:
+            m = np.maximum(m, np.float32(0))
+        e = np.where(visible, np.exp(s - m), 0.0).astype(np.float32)
+        den = e.sum(axis=-1, keepdims=True) + (np.exp(-m).astype(np.float32) if sink else np.float32(0))
+        out[:, h, :] = (e / den) @ v[:, h // group, :]
     return out
 
 

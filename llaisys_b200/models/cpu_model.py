@@ -7,7 +7,7 @@ CPU, float32, one sequence), and it serves here as the second implementation tha
 line's --test compares the engine's tokens with (test/test_infer.py:193-195 compares with a
 second implementation too), and as the model behind --device cpu.  It reads the same `ModelSpec`
 and the same tensors by name as the engine does, shares no code with the engine's parts or
-kernels, and knows the built-in part kinds only.
+kernels, and knows the built-in part kinds only (those of both built-in architectures).
 """
 from __future__ import annotations
 
@@ -18,8 +18,10 @@ import numpy as np
 from .. import cpu_ops
 from ..config.spec import ModelSpec, PartSpec
 
-_KNOWN = {"embedding": {"token_embedding"}, "norm": {"rms_norm"}, "mixer": {"gqa_attention"}, "ffn": {"swiglu_mlp"},
-          "block": {"pre_norm_residual"}, "head": {"lm_head"}, "position": {"rope_half_split"}}
+_KNOWN = {"embedding": {"token_embedding", "scaled_pair_embedding"}, "norm": {"rms_norm"},
+          "mixer": {"gqa_attention", "windowed_sink_attention"}, "ffn": {"swiglu_mlp", "routed_experts"},
+          "block": {"pre_norm_residual", "parallel_residual"}, "head": {"lm_head"},
+          "position": {"rope_half_split", "rope_leading"}}
 
 
 class CpuModel:
@@ -53,11 +55,65 @@ class CpuModel:
 
     def reset(self) -> None:
         self.length = 0
+        self.last_token = None                                       # the token before the next step's first (pair embedding)
         self.cache: List[dict] = [{} for _ in self.spec.order]       # per entry of the run order: mixer index -> (k, v)
 
     # ---- parts
     def _norm(self, p: PartSpec, x):
-        return cpu_ops.rms_norm(x, self.w[p.tensor_name("weight")], p.params["eps"])
+        return cpu_ops.rms_norm(x, self.w[p.tensor_name(p.params.get("tensor", "weight"))], p.params["eps"])
+
+    def _embed(self, tokens):
+        p = self.spec.embedding
+        ids = np.asarray(tokens)
+        if p.kind == "token_embedding":
+            return cpu_ops.embedding(ids, self.w[p.tensor_name("weight")]).astype(np.float32)
+        a = p.params
+        x = cpu_ops.embedding(ids, self.w[p.tensor_name(a.get("tensor", "weight"))]).astype(np.float32) * np.float32(a.get("scale", 1.0))
+        if a.get("pair"):
+            pr = a["pair"]
+            prev = np.concatenate([[self.last_token if self.last_token is not None else 0], ids[:-1]]).astype(np.int64)
+            rows = (prev * int(pr["mul_prev"]) + ids.astype(np.int64) * int(pr["mul_cur"])) % int(pr["buckets"])
+            if self.length == 0:
+                rows[0] = int(pr["buckets"])
+            x = cpu_ops.add(x, cpu_ops.embedding(rows, self.w[p.tensor_name(pr["tensor"])]))
+        self.last_token = int(ids[-1])
+        return x
+
+    def _sink_attention(self, p: PartSpec, x, positions, store: dict, key, owner):
+        a = p.params
+        nh, nkvh, dk, dv = a["num_heads"], a["num_kv_heads"], a["key_dim"], a["value_dim"]
+        n = dict({"q": "q", "k": "k", "v": "v", "o": "o"}, **(a.get("names") or {}))
+        T = x.shape[0]
+        pos = a.get("position")
+        rot = (lambda t: cpu_ops.rope_leading(t, positions, pos.params["dims"], pos.params["base"])) if pos is not None else (lambda t: t)
+        q = rot(cpu_ops.linear(x, self.w[p.tensor_name(n["q"])]).reshape(T, nh, dk))
+        if owner is None:
+            k = rot(cpu_ops.linear(x, self.w[p.tensor_name(n["k"])]).reshape(T, nkvh, dk))
+            v = cpu_ops.linear(x, self.w[p.tensor_name(n["v"])]).reshape(T, nkvh, dv)
+            old = store.get(key)
+            store[key] = (k, v) if old is None else (np.concatenate([old[0], k]), np.concatenate([old[1], v]))
+            ks, vs = store[key]
+        else:
+            ks, vs = owner[key]
+        o = cpu_ops.self_attention(q, ks, vs, a["scale"], a.get("window"), a.get("keep_first", 0), bool(a.get("sink")))
+        return cpu_ops.linear(o.reshape(T, nh * dv), self.w[p.tensor_name(n["o"])])
+
+    def _routed(self, p: PartSpec, x):
+        a = p.params
+        n = {"router": "router", "bias": "correction", "expert_up": "e{e}.up", "expert_down": "e{e}.down",
+             "shared_up": "shared.up", "shared_down": "shared.down", **(a.get("names") or {})}
+        bias = self.w[p.tensor_name(n["bias"])] if a.get("use_bias", True) else None
+        idx, wgt = cpu_ops.route_top(cpu_ops.linear(x, self.w[p.tensor_name(n["router"])]), bias, a["top"], a.get("route_scale", 1.0))
+        out = np.zeros((x.shape[0], a["hidden_size"]), dtype=np.float32)
+        for t in range(x.shape[0]):
+            for e, wt in zip(idx[t], wgt[t]):
+                up = self.w[p.tensor_name(n["expert_up"].format(e=int(e)))]
+                down = self.w[p.tensor_name(n["expert_down"].format(e=int(e)))]
+                out[t] += wt * cpu_ops.linear(cpu_ops.relu_squared(cpu_ops.linear(x[t:t + 1], up)), down)[0]
+        if a.get("shared_ff"):
+            out = cpu_ops.add(out, cpu_ops.linear(cpu_ops.relu_squared(cpu_ops.linear(x, self.w[p.tensor_name(n["shared_up"])])),
+                                                  self.w[p.tensor_name(n["shared_down"])]))
+        return out
 
     def _attention(self, p: PartSpec, x, positions, store: dict, key, owner):
         a = p.params
@@ -89,21 +145,26 @@ class CpuModel:
     def step(self, tokens: Sequence[int]) -> np.ndarray:
         """Feeds the next tokens of the sequence; returns float32 logits [len(tokens), vocab]."""
         positions = np.arange(self.length, self.length + len(tokens))
-        x = cpu_ops.embedding(np.asarray(tokens), self.w[self.spec.embedding.tensor_name("weight")]).astype(np.float32)
+        x = self._embed(tokens)
         for c, call in enumerate(self.spec.order):
             owner = self.cache[call.cache_of] if call.cache_of is not None else None
             m = 0
-            for sub in self.spec.layers[call.layer].sublayers:
-                h = self._norm(sub.norm, x) if sub.norm is not None else x
+            layer = self.spec.layers[call.layer]
+            parallel = layer.block == "parallel_residual"          # every sub-layer reads the stream as the layer found it
+            x_in = x
+            for sub in layer.sublayers:
+                src = x_in if parallel else x
+                h = self._norm(sub.norm, src) if sub.norm is not None else src
                 if sub.category == "mixer":
-                    x = cpu_ops.add(self._attention(sub.part, h, positions, self.cache[c], m, owner), x)
+                    attend = self._sink_attention if sub.part.kind == "windowed_sink_attention" else self._attention
+                    x = cpu_ops.add(attend(sub.part, h, positions, self.cache[c], m, owner), x)
                     m += 1
                 else:
-                    x = cpu_ops.add(self._mlp(sub.part, h), x)
+                    x = cpu_ops.add((self._routed if sub.part.kind == "routed_experts" else self._mlp)(sub.part, h), x)
         self.length += len(tokens)
         x = self._norm(self.spec.final_norm, x)
         head = self.spec.head
-        name = head.params.get("tied_to") or head.tensor_name("weight")
+        name = head.params.get("tied_to") or head.tensor_name(head.params.get("tensor", "weight"))
         return cpu_ops.linear(x, self.w[name])
 
     def generate(self, prompt: Sequence[int], max_new_tokens: int, stop_ids: Sequence[int] = ()) -> List[int]:

@@ -344,6 +344,26 @@ def test_greedy_generation_through_the_entry_point_and_scheduler(tmp_path):
     assert not model.engine.cache.live_slots
 
 
+def test_command_line(tmp_path):
+    """python -m llaisys_b200.cli on a model folder of this design: --test compares the engine's tokens with those of
+    the package's CPU model; --random-weights writes a folder from a configuration first."""
+    import os
+    import sys
+    env = dict(os.environ, PYTHONPATH=str(ROOT))
+    folder = vh.make_folder(tmp_path / "m", vh.CONFIGS["P"], seed=17, attn_gain=8.0)
+    (tmp_path / "batch.txt").write_text("5,17,3,200,7,7,7,7,7\n[9, 8]\n1\n")
+    out = subprocess.run([sys.executable, "-m", "llaisys_b200.cli", "--model", str(folder), "--batch-file", str(tmp_path / "batch.txt"),
+                          "--max_steps", "6", "--test", "--dtype", "float32"], env=env, capture_output=True, text=True, timeout=600)
+    assert out.returncode == 0, out.stderr[-2000:]
+    assert out.stdout.count("Tokens:") == 3 and "Test passed" in out.stdout
+    cfg = tmp_path / "cfg.json"
+    cfg.write_text(json.dumps(vh.CONFIGS["R"]))
+    out = subprocess.run([sys.executable, "-m", "llaisys_b200.cli", "--random-weights", str(cfg), "--seed", "3", "--tokens", "1,2,3",
+                          "--max_steps", "4", "--test", "--dtype", "bfloat16"], env=env, capture_output=True, text=True, timeout=600)
+    assert out.returncode == 0, out.stderr[-2000:]
+    assert "Test passed" in out.stdout
+
+
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_replay_of_a_trace(tmp_path, dtype):
     td = torch.float32 if dtype == "float32" else torch.bfloat16

@@ -142,3 +142,19 @@ def test_the_oracle_one_function_at_a_time():
     gate = 1 / (1 + np.exp(-(h @ w["router"].T)))[0]
     # the correction decides the choice (expert 1), the weight is the plain gate times the scale
     assert np.allclose(out[0], 2.0 * gate[1] * (np.maximum(h @ w["e1.up"].T, 0) ** 2 @ w["e1.down"].T)[0])
+
+
+def test_the_cpu_model_serves_the_design(tmp_path):
+    """The package's own CPU model (float32 numpy operators; what `--device cpu` and `--test` of the command line run)
+    against the plain oracle, prompt in one step and then token by token."""
+    from llaisys_b200.models.cpu_model import CpuModel
+    for name in ("P", "R"):
+        cfg = vh.CONFIGS[name]
+        folder = vh.make_folder(tmp_path / name, cfg, seed=3, attn_gain=8.0)
+        oracle = vh.Oracle(folder)
+        tokens = vh.random_requests(cfg, [90], seed=2)[0]
+        model = CpuModel.from_folder(folder)
+        got = np.concatenate([model.step(tokens[:70])] + [model.step([t]) for t in tokens[70:]])
+        assert np.abs(got - oracle.logits(tokens)).max() < 2e-4
+        new = model.generate(tokens[:5], 4)
+        assert len(new) == 4 and new[0] == int(np.argmax(oracle.logits(tokens[:5])[-1]))
