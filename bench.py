@@ -498,19 +498,19 @@ def design_configs(size: str, layers: int):
     vocab = 32768
 
     def mixer(kv_from=None):
-        m = {"heads": H, "kv_heads": G, "dim": dh, "vdim": dh, "scale": dh ** -0.5, "rot": {"dims": rot, "base": 500000.0},
+        m = {"heads": H, "kv_heads": G, "dim": dh, "vdim": dh, "scale": dh ** -0.5, "rot": {"dims": rot, "base": 1000000.0},
              "mask": {"size": window, "keep_first": keep}}
         if kv_from is not None:
             m["kv_from"] = kv_from
         return m
 
-    mlp = {"kind": "moe", "router": {"experts": E, "top": top, "scale": 1.5}, "expert": {"ff": ff}, "shared": {"ff": sff}}
+    mlp = {"kind": "moe", "router": {"experts": E, "top": top, "scale": 2.5}, "expert": {"ff": ff}, "shared": {"ff": sff}}
     vz_layers = []
     for i in range(layers):
         reads = i % 2 == 1                     # every second layer reads the keys and values of the layer before it
         vz_layers.append({"type": "attention", "mixer": mixer(i - 1 if reads else None), "mlp": mlp})
     vz = {"architecture": "Vumezen", "vocab": vocab, "width": D, "norm": {"eps": 1e-6},
-          "embedding": {"scale": 1.0, "bigram": {"buckets": 65521, "mul_prev": 31, "mul_cur": 17}}, "layers": vz_layers}
+          "embedding": {"scale": 1.0, "bigram": {"buckets": 65521, "mul_prev": 1000003, "mul_cur": 8191}}, "layers": vz_layers}
     inter = (2 * (top * ff + sff) // 3 + 127) // 128 * 128
     qw = dict(QWEN2_1_5B, num_hidden_layers=layers, hidden_size=D, num_attention_heads=H, num_key_value_heads=G, head_dim=dh,
               intermediate_size=inter, vocab_size=vocab, use_sliding_window=False)

@@ -43,9 +43,9 @@ def config(vocab, width, layers, scale=1.0, bigram=None, eps=1e-5):
 #    without a feed-forward, every expert chosen (the routing that 16-bit rounding cannot flip).
 CONFIGS = {
     "P": config(211, 64, [
-        layer(4, 2, 16, 24, 8, 70, 3, moe=moe(6, 2, 40, 24, scale=1.5)),
-        layer(4, 2, 16, 24, 8, 33, 5, kv_from=0, moe=moe(6, 2, 40, 24, scale=1.5)),
-        layer(2, 1, 32, 16, 32, 70, 3, moe=moe(5, 3, 24, 48, scale=0.7), base=500000.0),
+        layer(4, 2, 16, 24, 8, 70, 3, moe=moe(6, 2, 40, 24, scale=1.25)),
+        layer(4, 2, 16, 24, 8, 33, 5, kv_from=0, moe=moe(6, 2, 40, 24, scale=1.25)),
+        layer(2, 1, 32, 16, 32, 70, 3, moe=moe(5, 3, 24, 48, scale=0.7), base=250000.0),
     ], scale=3.5, bigram=(97, 7, 13)),
     "Q": config(150, 44, [
         layer(3, 3, 18, 18, 18, 1000, 0, moe=moe(4, 1, 20)),
