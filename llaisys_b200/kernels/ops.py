@@ -874,7 +874,14 @@ def moe_route(x: torch.Tensor, router: torch.Tensor, bias: Optional[torch.Tensor
     E = router.shape[0]
     assert router.shape == (E, H) and router.is_contiguous() and x.stride(1) == 1
     assert bias is None or (bias.dtype == torch.float32 and bias.numel() == E)
-    z = linear(x, router, out_dtype=torch.float32)
+    plan = None
+    if T > 256 and _tc_ok(x, router, None):
+        # many tokens against a handful of rows: tiles of 64 tokens and the K range cut over a cluster, so that the
+        # product runs on more than T / 256 blocks
+        tiles, kblocks = -(-T // 64) * -(-E // 128), -(-H // 64)
+        splits = max([s for s in (1, 2, 4, 8) if s == 1 or (tiles * s <= 2 * _sm_count(x.device) and s <= kblocks // 2)])
+        plan = (64, splits)
+    z = linear(x, router, out_dtype=torch.float32, plan=plan)
     idx = torch.empty((T, top), dtype=torch.int32, device=x.device)
     wgt = torch.empty((T, top), dtype=torch.float32, device=x.device)
     f = _fn(_moe_lib(), "llb_moe_select", [c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_float, c_void_p, c_void_p, c_void_p])
