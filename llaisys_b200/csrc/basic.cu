@@ -872,8 +872,28 @@ __global__ void relu_squared_kernel(T* __restrict__ x, size_t n) {
     x[i] = from_f32<T>(v * v);
 }
 
+// bfloat16, eight elements (16 bytes) per thread
+__global__ void relu_squared_vec_kernel(bf16* __restrict__ x, size_t n8) {
+    llb_grid_dependency_sync();
+    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n8) return;
+    uint4 v = reinterpret_cast<uint4*>(x)[i];
+    bf16* e = reinterpret_cast<bf16*>(&v);
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+        float f = fmaxf(to_f32(e[k]), 0.f);
+        e[k] = from_f32<bf16>(f * f);
+    }
+    reinterpret_cast<uint4*>(x)[i] = v;
+}
+
 LLB_API int llb_relu_squared(void* x, int dtype, long long n, cudaStream_t stream) {
     if (n <= 0) return 0;
+    if (dtype == LLB_BF16 && n % 8 == 0 && !((uintptr_t)x & 15)) {
+        const size_t n8 = (size_t)n / 8;
+        llb_launch(relu_squared_vec_kernel, dim3((unsigned)((n8 + 255) / 256)), dim3(256), 0, stream, (bf16*)x, n8);
+        return llb_status();
+    }
     LLB_DISPATCH_DTYPE(dtype, TT,
         llb_launch(relu_squared_kernel<TT>, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, stream, (TT*)x, (size_t)n));
     return llb_status();

@@ -85,9 +85,14 @@ moe_plan_kernel(const int* __restrict__ idx, int N, int E, int tile_rows, int* _
     for (int e = tid; e < E; e += blockDim.x) count[e] = cursor[e] = 0;
     llb_grid_dependency_sync();
     __syncthreads();
-    for (int i = tid; i < N; i += blockDim.x) {
-        const int e = idx[i];
-        if (e >= 0 && e < E) atomicAdd(&count[e], 1);
+    // (four pairs per thread and round: the block is alone on the device, so its loads have to be in flight together)
+    for (int i0 = tid; i0 < N; i0 += 4 * blockDim.x) {
+        int e4[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) e4[u] = i0 + u * blockDim.x < N ? idx[i0 + u * blockDim.x] : -1;
+#pragma unroll
+        for (int u = 0; u < 4; ++u)
+            if (e4[u] >= 0 && e4[u] < E) atomicAdd(&count[e4[u]], 1);
     }
     __syncthreads();
     if (tid == 0) {
@@ -109,12 +114,18 @@ moe_plan_kernel(const int* __restrict__ idx, int N, int E, int tile_rows, int* _
             tiles[2 * max_tiles + i] = min(tile_rows, count[e] - r);
         }
     }
-    for (int i = tid; i < N; i += blockDim.x) {
-        const int e = idx[i];
-        if (e < 0 || e >= E) continue;
-        const int s = first[e] + atomicAdd(&cursor[e], 1);
-        slot_of[i] = s;
-        pair_of[s] = i;
+    for (int i0 = tid; i0 < N; i0 += 4 * blockDim.x) {
+        int e4[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) e4[u] = i0 + u * blockDim.x < N ? idx[i0 + u * blockDim.x] : -1;
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const int e = e4[u], i = i0 + u * blockDim.x;
+            if (e < 0 || e >= E) continue;
+            const int s = first[e] + atomicAdd(&cursor[e], 1);
+            slot_of[i] = s;
+            pair_of[s] = i;
+        }
     }
 }
 
