@@ -2,6 +2,7 @@ from .spec import CallSpec, ConfigError, LayerSpec, ModelSpec, PartSpec, SubLaye
 from .registry import config_from_dict, known_architectures, load_config, register_architecture
 from .qwen2 import Qwen2Config
 from .vumezen import VumezenConfig
+from .nubedra import NubedraConfig
 
-__all__ = ["CallSpec", "ConfigError", "LayerSpec", "ModelSpec", "PartSpec", "SubLayerSpec", "Qwen2Config", "VumezenConfig",
+__all__ = ["CallSpec", "ConfigError", "LayerSpec", "ModelSpec", "PartSpec", "SubLayerSpec", "Qwen2Config", "VumezenConfig", "NubedraConfig",
            "config_from_dict", "known_architectures", "load_config", "register_architecture"]

@@ -28,19 +28,22 @@ class PartSpec:
 
 @dataclass(frozen=True)
 class SubLayerSpec:
-    """One step of a layer: a part of category `category` ("mixer" or "ffn") behind an optional norm."""
+    """One step of a layer: a part of category `category` ("mixer" or "ffn") behind an optional norm; `post_norm`,
+    for arrangements that have one, is a norm of the part's output before it joins the stream."""
     category: str
     part: PartSpec
     norm: Optional[PartSpec] = None
+    post_norm: Optional[PartSpec] = None
 
 
 @dataclass(frozen=True)
 class LayerSpec:
     """A layer is an arrangement (`block`) of sub-layers around the residual stream: as many as
     the architecture has (mixer then feed-forward here; a mixer alone, or a mixer and two
-    feed-forwards, are other layers of the same kind)."""
+    feed-forwards, are other layers of the same kind).  `params`: constants of the arrangement itself."""
     block: str
     sublayers: Tuple[SubLayerSpec, ...]
+    params: Mapping[str, Any] = field(default_factory=dict)
 
     @classmethod
     def pair(cls, block: str, mixer: PartSpec, mixer_norm: PartSpec, ffn: PartSpec, ffn_norm: PartSpec) -> "LayerSpec":

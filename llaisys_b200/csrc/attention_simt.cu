@@ -8,7 +8,10 @@
 // A window W > 0 (not in that project) further restricts the keys to p - W < t <= p; with keep_first F > 0
 // the keys t < F stay visible behind the window (at their true positions).  With `sink` the softmax has one
 // more term of score 0 that carries no value: weights e^{s_t} / (1 + sum e^{s_t}).  Values may have a width
-// of their own (-DLLB_VALUE_DIM, default the head size).
+// of their own (-DLLB_VALUE_DIM, default the head size).  `sink_logits` gives the sink a learned score per query
+// head instead of 0 (the term e^{sink_h}).  With `v_in_k` the values are the leading LLB_VALUE_DIM elements of the key
+// rows themselves (a cache of one latent row per token that serves as key and as value; no value pool is read).
+// `kv_row_stride` > 0: the step's own keys (and values) stand in a buffer of their own with that row stride.
 //
 // Keys are walked in tiles of one cache page with an online softmax, so nothing of size
 // [queries, keys] is ever stored.
@@ -31,7 +34,7 @@
 
 constexpr int DH = LLB_HEAD_DIM;     // query / key width
 constexpr int DV = LLB_VALUE_DIM;    // value and output width
-constexpr int ROWS = 32;            // query rows of a block
+constexpr int ROWS = DH > 256 ? 8 : 32;   // query rows of a block (fewer for very wide keys, so that a tile still fits)
 constexpr int WARPS = 4;
 constexpr int RPW = ROWS / WARPS;   // rows of a warp
 constexpr int DPL = (DV + 31) / 32; // output dims of a lane
@@ -59,6 +62,9 @@ struct AttnParams {
     int keep_first;       // with a window: keys before this position stay visible
     int pinned;           // pages ahead of the ring that are never overwritten
     int sink;             // the softmax's denominator has one more term e^0
+    const float* sink_logits;   // [nh] or null: the sink's score per query head instead of 0 (implies a sink)
+    int v_in_k;           // values are the first DV elements of the key rows; vpool and v_new are not read
+    int kv_row_stride;    // row stride of k_new / v_new when they are no part of the q buffer (0: row_stride)
 };
 
 template <typename T, bool DECODE>
@@ -66,8 +72,11 @@ __global__ void __launch_bounds__(WARPS * 32) attn_kernel(AttnParams p) {
     extern __shared__ float smem[];
     float* Qs = smem;                        // [ROWS][DH]
     float* Ks = Qs + ROWS * DH;              // [LLB_PAGE][DH + 1]
-    float* Vs = Ks + LLB_PAGE * (DH + 1);    // [LLB_PAGE][DV]
-    float* Ps = Vs + LLB_PAGE * DV;          // [WARPS][LLB_PAGE]
+    float* Vs = Ks + LLB_PAGE * (DH + 1);    // [LLB_PAGE][DV]; with v_in_k the key tile itself
+    float* Ps = Vs + (p.v_in_k ? 0 : LLB_PAGE * DV);   // [WARPS][LLB_PAGE]
+    const int vs_stride = p.v_in_k ? DH + 1 : DV;
+    if (p.v_in_k) Vs = Ks;
+    const int kv_stride = p.kv_row_stride > 0 ? p.kv_row_stride : p.row_stride;
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int b = blockIdx.z;
@@ -117,12 +126,13 @@ __global__ void __launch_bounds__(WARPS * 32) attn_kernel(AttnParams p) {
         it_lo = blockIdx.x * chunk;
         it_hi = min(it_hi, it_lo + chunk);
     }
-    const bool with_sink = p.sink && (!DECODE || blockIdx.x == 0);
+    const bool with_sink = (p.sink || p.sink_logits) && (!DECODE || blockIdx.x == 0);
 
     float m[RPW], l[RPW], o[RPW][DPL];
 #pragma unroll
     for (int i = 0; i < RPW; ++i) {
-        m[i] = with_sink ? 0.f : -INFINITY;
+        const int r = warp + i * WARPS;
+        m[i] = with_sink ? (p.sink_logits ? p.sink_logits[row_head0 + (DECODE ? min(r, n_rows - 1) : 0)] : 0.f) : -INFINITY;
         l[i] = with_sink ? 1.f : 0.f;
 #pragma unroll
         for (int e = 0; e < DPL; ++e) o[i][e] = 0.f;
@@ -142,19 +152,19 @@ __global__ void __launch_bounds__(WARPS * 32) attn_kernel(AttnParams p) {
             float kv = 0.f;
             if ((kp >= key_lo || kp < keep) && kp <= last_pos) {
                 if (!DECODE && !p.all_from_cache && kp >= len_before)
-                    kv = to_f32(knew[(size_t)(tok0 + kp - len_before) * p.row_stride + kvh * DH + d]);
+                    kv = to_f32(knew[(size_t)(tok0 + kp - len_before) * kv_stride + kvh * DH + d]);
                 else
                     kv = to_f32(kpool[paged_row(table, p.ring, kp, kvh, p.nkvh, DH, p.pinned) + d]);
             }
             Ks[j * (DH + 1) + d] = kv;
         }
-        for (int i = tid; i < LLB_PAGE * DV; i += WARPS * 32) {
+        for (int i = tid; i < (p.v_in_k ? 0 : LLB_PAGE * DV); i += WARPS * 32) {
             int j = i / DV, d = i - j * DV;
             int kp = tile * LLB_PAGE + j;
             float vv = 0.f;
             if ((kp >= key_lo || kp < keep) && kp <= last_pos) {
                 if (!DECODE && !p.all_from_cache && kp >= len_before)
-                    vv = to_f32(vnew[(size_t)(tok0 + kp - len_before) * p.row_stride + kvh * DV + d]);
+                    vv = to_f32(vnew[(size_t)(tok0 + kp - len_before) * kv_stride + kvh * DV + d]);
                 else
                     vv = to_f32(vpool[paged_row(table, p.ring, kp, kvh, p.nkvh, DV, p.pinned) + d]);
             }
@@ -198,7 +208,7 @@ __global__ void __launch_bounds__(WARPS * 32) attn_kernel(AttnParams p) {
                 if (d < DV) {
                     float acc = o[i][e] * alpha;
 #pragma unroll 8
-                    for (int j = 0; j < LLB_PAGE; ++j) acc = fmaf(ps[j], Vs[j * DV + d], acc);
+                    for (int j = 0; j < LLB_PAGE; ++j) acc = fmaf(ps[j], Vs[j * vs_stride + d], acc);
                     o[i][e] = acc;
                 }
             }
@@ -260,17 +270,18 @@ __global__ void attn_combine_kernel(T* __restrict__ out, const float* __restrict
     }
 }
 
-static size_t attn_smem_bytes() {
-    return (size_t)(ROWS * DH + LLB_PAGE * (DH + 1) + LLB_PAGE * DV + WARPS * LLB_PAGE) * sizeof(float);
+static size_t attn_smem_bytes(bool v_in_k) {
+    return (size_t)(ROWS * DH + LLB_PAGE * (DH + 1) + (v_in_k ? 0 : LLB_PAGE * DV) + WARPS * LLB_PAGE) * sizeof(float);
 }
 
 template <typename T, bool DECODE>
 static int launch_attn(const AttnParams& p, dim3 grid, cudaStream_t stream) {
     auto k = attn_kernel<T, DECODE>;
-    size_t smem = attn_smem_bytes();
+    size_t smem = attn_smem_bytes(p.v_in_k != 0);
     static bool configured = false;          // once per instantiation: not repeated inside a graph capture
-    if (!configured && smem > 48 * 1024) {
-        cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (!configured && attn_smem_bytes(false) > 48 * 1024) {
+        cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             (int)(p.v_in_k && attn_smem_bytes(false) > 227 * 1024 ? smem : attn_smem_bytes(false)));
         if (e != cudaSuccess) return (int)e;
     }
     configured = true;

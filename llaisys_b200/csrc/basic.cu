@@ -900,4 +900,108 @@ LLB_API int llb_relu_squared(void* x, int dtype, long long n, cudaStream_t strea
 }
 
 // ------------------------------------------------------------------ misc
+
+// ------------------------------------------------------------------ a part's normed output into the stream (+ the next norm)
+// residual[r] += mult * delta[r] / sqrt(mean(delta[r]^2) + eps) * (w_post + offset), all in float32; with `out` the same
+// pass then normalises the new stream row with w_next: out[r] = residual[r] / sqrt(mean(residual[r]^2) + eps) *
+// (w_next + offset), so that a layer whose parts sit between two norms needs one launch per part for its norms.
+// Without delta only the second half runs (the plain norm of a row).  The row lives in shared memory (H floats).
+template <typename TD, typename TW, typename TO>
+__global__ void __launch_bounds__(256)
+scaled_norm_add_kernel(float* __restrict__ residual, const TD* __restrict__ delta, const TW* __restrict__ w_post,
+                       float mult, const TW* __restrict__ w_next, TO* __restrict__ out, int H, float eps, float offset) {
+    extern __shared__ float rowbuf[];
+    __shared__ float red[8];
+    const int r = blockIdx.x, tid = threadIdx.x, lane = tid & 31, wp = tid >> 5;
+    llb_grid_dependency_sync();
+    float* res = residual + (size_t)r * H;
+    if (delta) {
+        const TD* d = delta + (size_t)r * H;
+        float ss = 0.f;
+        for (int j = tid; j < H; j += 256) {
+            float v = to_f32(d[j]);
+            rowbuf[j] = v;
+            ss += v * v;
+        }
+        ss = warp_sum(ss);
+        if (lane == 0) red[wp] = ss;
+        __syncthreads();
+        float tot = 0.f;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) tot += red[i];
+        const float inv = mult / sqrtf(tot / (float)H + eps);
+        __syncthreads();
+        for (int j = tid; j < H; j += 256) {
+            float v = res[j] + rowbuf[j] * inv * (to_f32(w_post[j]) + offset);
+            res[j] = v;
+            rowbuf[j] = v;
+        }
+    } else {
+        for (int j = tid; j < H; j += 256) rowbuf[j] = res[j];
+    }
+    if (!out) return;
+    float ss = 0.f;
+    for (int j = tid; j < H; j += 256) ss += rowbuf[j] * rowbuf[j];
+    ss = warp_sum(ss);
+    if (lane == 0) red[wp] = ss;
+    __syncthreads();
+    float tot = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) tot += red[i];
+    const float inv = 1.0f / sqrtf(tot / (float)H + eps);
+    for (int j = tid; j < H; j += 256)
+        out[(size_t)r * H + j] = from_f32<TO>(rowbuf[j] * inv * (to_f32(w_next[j]) + offset));
+}
+
+LLB_API int llb_scaled_norm_add(float* residual, const void* delta, int delta_dtype, const void* w_post, float mult,
+                                const void* w_next, int w_dtype, void* out, int out_dtype, int R, int H, float eps,
+                                float offset, cudaStream_t stream) {
+    if (R == 0) return 0;
+    size_t smem = (size_t)H * sizeof(float);
+    if (smem > 200 * 1024) return (int)cudaErrorInvalidValue;
+    if (!delta) delta_dtype = LLB_F32;
+    if (!out) out_dtype = LLB_F32;
+    LLB_DISPATCH_DTYPE(delta_dtype, TD, {
+        LLB_DISPATCH_DTYPE(w_dtype, TW, {
+            LLB_DISPATCH_DTYPE(out_dtype, TO, {
+                auto k = scaled_norm_add_kernel<TD, TW, TO>;
+                if (smem > 48 * 1024) cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+                llb_launch(k, dim3(R), dim3(256), smem, stream, residual, (const TD*)delta, (const TW*)w_post, mult,
+                           (const TW*)w_next, (TO*)out, H, eps, offset);
+            });
+        });
+    });
+    return llb_status();
+}
+
+// ------------------------------------------------------------------ gated activation of a fused gate/up product
+// gate_up is [T, 2I] with the gate columns first; out[t, i] = act(gate) * up, act: 0 silu, 1 relu, 2 gelu (tanh form).
+template <typename TI, typename TO>
+__global__ void glu_kernel(TO* __restrict__ out, const TI* __restrict__ gate_up, int I, size_t n, int act) {
+    llb_grid_dependency_sync();
+    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    size_t t = i / I;
+    int c = (int)(i - t * I);
+    float g = to_f32(gate_up[t * 2 * I + c]);
+    float u = to_f32(gate_up[t * 2 * I + I + c]);
+    float a;
+    if (act == 1) a = fmaxf(g, 0.f);
+    else if (act == 2) a = 0.5f * g * (1.0f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g)));
+    else a = g / (1.0f + expf(-g));
+    out[i] = from_f32<TO>(a * u);
+}
+
+LLB_API int llb_glu(void* out, int out_dtype, const void* gate_up, int in_dtype, int T, int I, int act, cudaStream_t stream) {
+    size_t n = (size_t)T * I;
+    if (n == 0) return 0;
+    LLB_DISPATCH_DTYPE(in_dtype, TI, {
+        LLB_DISPATCH_DTYPE(out_dtype, TO, {
+            llb_launch(glu_kernel<TI, TO>, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, stream, (TO*)out,
+                       (const TI*)gate_up, I, n, act);
+        });
+    });
+    return llb_status();
+}
+
 LLB_API const char* llb_error_string(int code) { return cudaGetErrorString((cudaError_t)code); }

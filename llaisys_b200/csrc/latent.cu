@@ -1,0 +1,260 @@
+// Row-wise kernels of latent attention: queries, keys and values all pass through low-rank latents, and what a token
+// leaves in the cache is one row [latent c (kv_rank) | rotated shared key part (rope_dim)] for all heads together.
+//
+// Since a head's unrotated key is W_uk[h] c and its value W_uv[h] c, the score q_n . (W_uk[h] c) equals
+// (W_uk[h]^T q_n) . c and the head's output is W_uv[h] (sum_t p_t c_t): attention runs over the cached rows themselves,
+// as one key/value head that every query head shares, with the query carried into the latent space first and the
+// latent result carried into the head's value space afterwards.
+//
+//  * latent_prep: per token, from the fused down projections: RMS norm (plain weight) of the query latent; RMS norm
+//    of the key/value latent; rotation of the shared key part (pairs (2i, 2i+1), angles from float32 tables that
+//    already hold any rescaling of frequency and magnitude); the row [c | rotated part] is written densely for the
+//    step's attention and, with `append`, into the token's row of the paged cache.
+//  * latent_append: the same rows into the paged cache as a pass of its own (a ring cache is appended to after the
+//    step's attention).
+//  * head_matmul: y[t, h, :] = x[t, h, :] M[h]  (M [heads, in, out]) with float32 accumulation: the query's unrotated
+//    part into the latent space, the latent result into the value space; optional tail: rotation of the `tail`
+//    elements that follow x[t, h, :in] into y[t, h, out:]; optional per-(token, head) factor sigmoid(gate[t, h]).
+#include "common.cuh"
+
+struct LatentPrepParams {
+    const void* proj;         // [T, row_stride]
+    int row_stride;
+    int q_off, q_rank;        // the query latent's columns
+    int kv_off, kv_rank;      // the key/value latent's columns (kv_rank 0: the layer projects none)
+    int kr_off, rope_dim;     // the shared key part's columns
+    int rot;                  // rotated dimensions (<= rope_dim, even)
+    const void* wq;           // [q_rank] norm weight
+    const void* wkv;          // [kv_rank]
+    float eps;
+    const float* cos_t;       // [table_rows, rot / 2]
+    const float* sin_t;
+    int table_rows;
+    const int* tok_pos;
+    void* q_out;              // [T, q_rank]
+    void* kv_out;             // [T, kv_rank + rope_dim]
+    // append
+    int append;
+    const int* tok_seq;
+    const int* seq_start;
+    const int* seq_len_before;
+    void* pool;               // [pages, 1, LLB_PAGE, kv_rank + rope_dim]
+    const int* page_table;
+    int table_stride, ring, pinned;
+    int* err;
+};
+
+template <typename T, typename TW>
+__global__ void __launch_bounds__(256) latent_prep_kernel(LatentPrepParams p) {
+    __shared__ float red[8];
+    const int t = blockIdx.x, tid = threadIdx.x, lane = tid & 31, wp = tid >> 5;
+    const int pos = p.tok_pos[t];
+    if (p.kv_rank > 0 && p.rot > 0 && (pos < 0 || pos >= p.table_rows)) {
+        if (tid == 0) atomicExch(p.err, 2);
+        return;
+    }
+    llb_grid_dependency_sync();
+    const T* row = (const T*)p.proj + (size_t)t * p.row_stride;
+    // ---- the query latent
+    {
+        float ss = 0.f;
+        for (int j = tid; j < p.q_rank; j += 256) {
+            float v = to_f32(row[p.q_off + j]);
+            ss += v * v;
+        }
+        ss = warp_sum(ss);
+        if (lane == 0) red[wp] = ss;
+        __syncthreads();
+        float tot = 0.f;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) tot += red[i];
+        const float inv = 1.0f / sqrtf(tot / (float)p.q_rank + p.eps);
+        T* qo = (T*)p.q_out + (size_t)t * p.q_rank;
+        const TW* w = (const TW*)p.wq;
+        for (int j = tid; j < p.q_rank; j += 256) qo[j] = from_f32<T>(to_f32(row[p.q_off + j]) * inv * to_f32(w[j]));
+    }
+    if (p.kv_rank <= 0) return;
+    // ---- the key/value latent and the shared key part
+    __syncthreads();
+    float ss = 0.f;
+    for (int j = tid; j < p.kv_rank; j += 256) {
+        float v = to_f32(row[p.kv_off + j]);
+        ss += v * v;
+    }
+    ss = warp_sum(ss);
+    if (lane == 0) red[wp] = ss;
+    __syncthreads();
+    float tot = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) tot += red[i];
+    const float inv = 1.0f / sqrtf(tot / (float)p.kv_rank + p.eps);
+    const int width = p.kv_rank + p.rope_dim;
+    T* dense = (T*)p.kv_out + (size_t)t * width;
+    T* paged = nullptr;
+    if (p.append) {
+        const int s = p.tok_seq[t];
+        const int last = p.seq_len_before[s] + (p.seq_start[s + 1] - p.seq_start[s]) - 1;
+        if (paged_survives(pos / LLB_PAGE, last / LLB_PAGE, p.ring, p.pinned))
+            paged = (T*)p.pool + paged_row(p.page_table + (size_t)s * p.table_stride, p.ring, pos, 0, 1, width, p.pinned);
+    }
+    const TW* w = (const TW*)p.wkv;
+    for (int j = tid; j < p.kv_rank; j += 256) {
+        T v = from_f32<T>(to_f32(row[p.kv_off + j]) * inv * to_f32(w[j]));
+        dense[j] = v;
+        if (paged) paged[j] = v;
+    }
+    const int half = p.rot >> 1;
+    for (int i = tid; i < half; i += 256) {
+        const float c = p.cos_t[(size_t)pos * half + i], s = p.sin_t[(size_t)pos * half + i];
+        const float a = to_f32(row[p.kr_off + 2 * i]), b = to_f32(row[p.kr_off + 2 * i + 1]);
+        T x = from_f32<T>(a * c - b * s), y = from_f32<T>(b * c + a * s);
+        dense[p.kv_rank + 2 * i] = x;
+        dense[p.kv_rank + 2 * i + 1] = y;
+        if (paged) {
+            paged[p.kv_rank + 2 * i] = x;
+            paged[p.kv_rank + 2 * i + 1] = y;
+        }
+    }
+    for (int j = p.rot + tid; j < p.rope_dim; j += 256) {
+        T v = row[p.kr_off + j];
+        dense[p.kv_rank + j] = v;
+        if (paged) paged[p.kv_rank + j] = v;
+    }
+}
+
+LLB_API int llb_latent_prep(LatentPrepParams p, int dtype, int w_dtype, int T, cudaStream_t stream) {
+    if (T == 0) return 0;
+    LLB_DISPATCH_DTYPE(dtype, TT, {
+        LLB_DISPATCH_DTYPE(w_dtype, TW, {
+            llb_launch(latent_prep_kernel<TT, TW>, dim3(T), dim3(256), 0, stream, p);
+        });
+    });
+    return llb_status();
+}
+
+// rows [T, width] -> the tokens' rows of the paged cache (one key head of `width` elements, no values)
+template <typename T>
+__global__ void __launch_bounds__(128) latent_append_kernel(const T* __restrict__ rows, int width, const int* __restrict__ tok_pos,
+                                                            const int* __restrict__ tok_seq, const int* __restrict__ seq_start,
+                                                            const int* __restrict__ seq_len_before, T* __restrict__ pool,
+                                                            const int* __restrict__ page_table, int table_stride, int ring,
+                                                            int pinned) {
+    const int t = blockIdx.x;
+    llb_grid_dependency_sync();
+    const int pos = tok_pos[t], s = tok_seq[t];
+    const int last = seq_len_before[s] + (seq_start[s + 1] - seq_start[s]) - 1;
+    if (!paged_survives(pos / LLB_PAGE, last / LLB_PAGE, ring, pinned)) return;
+    T* dst = pool + paged_row(page_table + (size_t)s * table_stride, ring, pos, 0, 1, width, pinned);
+    const T* src = rows + (size_t)t * width;
+    for (int j = threadIdx.x; j < width; j += blockDim.x) dst[j] = src[j];
+}
+
+LLB_API int llb_latent_append(const void* rows, int dtype, int T, int width, const int* tok_pos, const int* tok_seq,
+                              const int* seq_start, const int* seq_len_before, void* pool, const int* page_table,
+                              int table_stride, int ring, int pinned, cudaStream_t stream) {
+    if (T == 0) return 0;
+    LLB_DISPATCH_DTYPE(dtype, TT, {
+        llb_launch(latent_append_kernel<TT>, dim3(T), dim3(128), 0, stream, (const TT*)rows, width, tok_pos, tok_seq,
+                   seq_start, seq_len_before, (TT*)pool, page_table, table_stride, ring, pinned);
+    });
+    return llb_status();
+}
+
+// ------------------------------------------------------------------ per-head matrix product
+constexpr int HM_TOK = 16;        // tokens of a block
+constexpr int HM_COLS = 128;      // output columns of a block (one per thread)
+
+struct HeadMatmulParams {
+    const void* x;            // [T, x_stride]: head h's input at h * x_head
+    int x_stride, x_head;
+    const void* m;            // [H, n_in, n_out]
+    void* y;                  // [T, y_stride]: head h's output at h * y_head
+    int y_stride, y_head;
+    int T, H, n_in, n_out;
+    // tail: the `tail` elements after a head's n_in inputs go to y after its n_out outputs, the first `rot` of them
+    // rotated in pairs (2i, 2i+1) by the token's position
+    int tail, rot;
+    const float* cos_t;
+    const float* sin_t;
+    int table_rows;
+    const int* tok_pos;
+    // factor: y[t, h, :] *= sigmoid(gate[t * gate_stride + h])
+    const void* gate;
+    int gate_stride;
+    int* err;
+};
+
+template <typename T>
+__global__ void __launch_bounds__(HM_COLS) head_matmul_kernel(HeadMatmulParams p) {
+    extern __shared__ float xs[];                     // [HM_TOK][n_in]
+    const int tid = threadIdx.x, h = blockIdx.y;
+    const int t0 = blockIdx.x * HM_TOK, nt = min(HM_TOK, p.T - t0);
+    const int col = blockIdx.z * HM_COLS + tid;
+    llb_grid_dependency_sync();
+    const T* xb = (const T*)p.x;
+    for (int i = tid; i < nt * p.n_in; i += HM_COLS) {
+        int t = i / p.n_in, d = i - t * p.n_in;
+        xs[i] = to_f32(xb[(size_t)(t0 + t) * p.x_stride + h * p.x_head + d]);
+    }
+    __syncthreads();
+    T* yb = (T*)p.y;
+    if (col < p.n_out) {
+        float acc[HM_TOK];
+#pragma unroll
+        for (int t = 0; t < HM_TOK; ++t) acc[t] = 0.f;
+        const T* mh = (const T*)p.m + (size_t)h * p.n_in * p.n_out + col;
+        for (int d = 0; d < p.n_in; ++d) {
+            const float w = to_f32(mh[(size_t)d * p.n_out]);
+#pragma unroll
+            for (int t = 0; t < HM_TOK; ++t) acc[t] = fmaf(xs[t * p.n_in + d], w, acc[t]);   // rows past nt hold stale data, never stored
+        }
+#pragma unroll
+        for (int t = 0; t < HM_TOK; ++t) {
+            if (t < nt) {
+                float v = acc[t];
+                if (p.gate) {
+                    float g = to_f32(((const T*)p.gate)[(size_t)(t0 + t) * p.gate_stride + h]);
+                    v *= 1.0f / (1.0f + expf(-g));
+                }
+                yb[(size_t)(t0 + t) * p.y_stride + h * p.y_head + col] = from_f32<T>(v);
+            }
+        }
+    }
+    if (blockIdx.z == 0 && p.tail > 0) {
+        const int half = p.rot >> 1;
+        for (int i = tid; i < nt * half; i += HM_COLS) {
+            int t = i / half, j = i - t * half;
+            int pos = p.tok_pos[t0 + t];
+            if (pos < 0 || pos >= p.table_rows) {
+                atomicExch(p.err, 2);
+                continue;
+            }
+            const float c = p.cos_t[(size_t)pos * half + j], s = p.sin_t[(size_t)pos * half + j];
+            const T* src = xb + (size_t)(t0 + t) * p.x_stride + h * p.x_head + p.n_in;
+            T* dst = yb + (size_t)(t0 + t) * p.y_stride + h * p.y_head + p.n_out;
+            const float a = to_f32(src[2 * j]), b = to_f32(src[2 * j + 1]);
+            dst[2 * j] = from_f32<T>(a * c - b * s);
+            dst[2 * j + 1] = from_f32<T>(b * c + a * s);
+        }
+        const int rest = p.tail - p.rot;
+        for (int i = tid; i < nt * rest; i += HM_COLS) {
+            int t = i / rest, j = p.rot + i - t * rest;
+            yb[(size_t)(t0 + t) * p.y_stride + h * p.y_head + p.n_out + j] =
+                xb[(size_t)(t0 + t) * p.x_stride + h * p.x_head + p.n_in + j];
+        }
+    }
+}
+
+LLB_API int llb_head_matmul(HeadMatmulParams p, int dtype, cudaStream_t stream) {
+    if (p.T == 0 || p.H == 0) return 0;
+    size_t smem = (size_t)HM_TOK * (p.n_in > 0 ? p.n_in : 1) * sizeof(float);
+    if (smem > 200 * 1024) return (int)cudaErrorInvalidValue;
+    dim3 grid((p.T + HM_TOK - 1) / HM_TOK, p.H, p.n_out > 0 ? (p.n_out + HM_COLS - 1) / HM_COLS : 1);
+    if (grid.y > 65535 || grid.z > 65535) return (int)cudaErrorInvalidValue;
+    LLB_DISPATCH_DTYPE(dtype, TT, {
+        auto k = head_matmul_kernel<TT>;
+        if (smem > 48 * 1024) cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        llb_launch(k, grid, dim3(HM_COLS), smem, stream, p);
+    });
+    return llb_status();
+}

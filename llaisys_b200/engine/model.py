@@ -20,8 +20,9 @@ class DecoderModel:
                 if sub.category not in ("mixer", "ffn"):
                     raise ValueError(f"a sub-layer is a 'mixer' or an 'ffn', not {sub.category!r}")
                 norm = build_part("norm", sub.norm, env) if sub.norm is not None else None
-                subs.append(SubLayer(sub.category, build_part(sub.category, sub.part, env), norm))
-            self.blocks.append(part_class("block", ls.block)(subs, env))
+                post = build_part("norm", sub.post_norm, env) if sub.post_norm is not None else None
+                subs.append(SubLayer(sub.category, build_part(sub.category, sub.part, env), norm, post))
+            self.blocks.append(part_class("block", ls.block)(subs, env, ls.params))
         # Every mixer of every entry of the run order is a user of the cache with an index of its own.
         self.users: List[tuple] = []                 # user -> (order entry, layer, sub-layer index)
         self.call_users: List[tuple] = []            # order entry -> its users, in sub-layer order
@@ -86,6 +87,7 @@ class DecoderModel:
         for b in self.blocks:
             for sub in b.sublayers:
                 ps += ([sub.norm] if sub.norm is not None else []) + [sub.part]
+                ps += [sub.post_norm] if sub.post_norm is not None else []
         return ps + [self.final_norm, self.head]
 
     def expected_tensors(self) -> Dict[str, TensorDecl]:
@@ -132,5 +134,6 @@ class DecoderModel:
             residual, pending = self.blocks[call.layer].forward(residual, pending, ctx, self.call_users[c])
         if ctx.out_rows.numel() == 0:
             return None
-        h = self.final_norm.forward(residual, pending, rows=ctx.out_rows)
+        from ..parts.block import settle
+        h = settle(residual, pending, self.final_norm, rows=ctx.out_rows)
         return self.head.forward(h)

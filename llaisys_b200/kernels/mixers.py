@@ -1,0 +1,197 @@
+"""Python faces of the kernels of the recurrent and the latent mixers (csrc/gla.cu, csrc/latent.cu, and the CUDA-core
+attention kernel of csrc/attention_simt.cu run over a cache of latent rows)."""
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_float, c_int, c_void_p
+from typing import Optional
+
+import torch
+
+from ..csrc.build import load_module
+from .ops import DT, KernelError, _AttnParams, _attn_lib, _check, _dt, _fn, _need_cuda, _ptr, _stream
+
+
+class _GlaParams(ctypes.Structure):
+    _fields_ = [("q", c_void_p), ("k", c_void_p), ("v", c_void_p), ("row_stride", c_int), ("z", c_void_p), ("z_stride", c_int),
+                ("state", c_void_p), ("seq_start", c_void_p), ("seq_slot", c_void_p), ("out", c_void_p), ("H", c_int),
+                ("dk", c_int), ("dv", c_int), ("q_scale", c_float), ("inv_tau", c_float)]
+
+
+GLA_MAX_KEY_DIM = 256
+
+
+def gla_scan(proj: torch.Tensor, H: int, dk: int, dv: int, z: torch.Tensor, state: torch.Tensor, seq_start: torch.Tensor,
+             seq_slot: torch.Tensor, n_seqs: int, q_scale: float, decay_root: float) -> torch.Tensor:
+    """The gated-linear-attention recurrence over the new tokens of every sequence: proj [T, >= 2 H dk + H dv] holds the
+    heads' queries, then keys, then values; z [T, H dk] (float32) the decay logits; state [slots, H dk dv] (float32) is
+    read at row seq_slot[b] and left holding the state after the step.  Returns o [T, H dv] in float32."""
+    _need_cuda(proj, z, state)
+    assert z.dtype == torch.float32 and z.stride(1) == 1 and state.dtype == torch.float32 and state.is_contiguous()
+    assert proj.stride(1) == 1 and state.shape[1] == H * dk * dv
+    if dk > GLA_MAX_KEY_DIM:
+        raise KernelError(f"gated linear attention: {dk} key channels a head; the kernel takes up to {GLA_MAX_KEY_DIM}")
+    T = proj.shape[0]
+    out = torch.empty((T, H * dv), dtype=torch.float32, device=proj.device)
+    p = _GlaParams()
+    es = proj.element_size()
+    p.q, p.k, p.v = proj.data_ptr(), proj.data_ptr() + H * dk * es, proj.data_ptr() + 2 * H * dk * es
+    p.row_stride, p.z, p.z_stride = proj.stride(0), z.data_ptr(), z.stride(0)
+    p.state, p.seq_start, p.seq_slot, p.out = state.data_ptr(), seq_start.data_ptr(), seq_slot.data_ptr(), out.data_ptr()
+    p.H, p.dk, p.dv, p.q_scale, p.inv_tau = H, dk, dv, q_scale, 1.0 / decay_root
+    f = _fn(load_module("gla.cu"), "llb_gla_scan", [_GlaParams, c_int, c_int, c_void_p])
+    _check(f(p, _dt(proj), n_seqs, _stream()), "gated linear attention (recurrence)")
+    return out
+
+
+def gla_out(o: torch.Tensor, gate: torch.Tensor, weight: torch.Tensor, H: int, dv: int, eps: float,
+            out_dtype: torch.dtype) -> torch.Tensor:
+    """[T, H dv]: every head's o (float32) RMS-normed over its dv channels with `weight` [dv], times silu(gate) (gate a
+    [T, H dv] view with any row stride, in the output's dtype)."""
+    _need_cuda(o, gate, weight)
+    T = o.shape[0]
+    assert o.dtype == torch.float32 and o.is_contiguous() and gate.dtype == out_dtype and gate.stride(1) == 1
+    out = torch.empty((T, H * dv), dtype=out_dtype, device=o.device)
+    f = _fn(load_module("gla.cu"), "llb_gla_out", [c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int,
+                                                  c_int, c_float, c_void_p])
+    _check(f(_ptr(o), _ptr(gate), gate.stride(0), _ptr(weight), _dt(weight), _ptr(out), DT[out_dtype], T, H, dv, eps, _stream()),
+           "gated linear attention (head norm and gate)")
+    return out
+
+
+class _LatentPrepParams(ctypes.Structure):
+    _fields_ = [("proj", c_void_p), ("row_stride", c_int), ("q_off", c_int), ("q_rank", c_int), ("kv_off", c_int),
+                ("kv_rank", c_int), ("kr_off", c_int), ("rope_dim", c_int), ("rot", c_int), ("wq", c_void_p), ("wkv", c_void_p),
+                ("eps", c_float), ("cos_t", c_void_p), ("sin_t", c_void_p), ("table_rows", c_int), ("tok_pos", c_void_p),
+                ("q_out", c_void_p), ("kv_out", c_void_p), ("append", c_int), ("tok_seq", c_void_p), ("seq_start", c_void_p),
+                ("seq_len_before", c_void_p), ("pool", c_void_p), ("page_table", c_void_p), ("table_stride", c_int),
+                ("ring", c_int), ("pinned", c_int), ("err", c_void_p)]
+
+
+def latent_prep(proj: torch.Tensor, q_rank: int, kv_rank: int, rope_dim: int, wq: torch.Tensor, wkv: Optional[torch.Tensor],
+                eps: float, tables, tok_pos: torch.Tensor, err: torch.Tensor, append: Optional[dict] = None):
+    """From the fused down projections proj [T, q_rank (+ kv_rank + rope_dim) ...]: the RMS-normed query latent
+    [T, q_rank] and, when the layer projects its own (wkv given), the rows [normed latent | rotated shared key part]
+    [T, kv_rank + rope_dim]; tables = (cos, sin, rotated dims) or None.  append = dict(tok_seq, seq_start,
+    seq_len_before, pool, page_table, ring, pinned) also writes those rows into the paged cache."""
+    _need_cuda(proj, wq, wkv, tok_pos)
+    T = proj.shape[0]
+    assert proj.stride(1) == 1 and tok_pos.numel() == T
+    own = wkv is not None
+    q_out = torch.empty((T, q_rank), dtype=proj.dtype, device=proj.device)
+    kv_out = torch.empty((T, kv_rank + rope_dim), dtype=proj.dtype, device=proj.device) if own else None
+    p = _LatentPrepParams()
+    p.proj, p.row_stride, p.q_off, p.q_rank = proj.data_ptr(), proj.stride(0), 0, q_rank
+    p.kv_off, p.kv_rank, p.kr_off, p.rope_dim = q_rank, kv_rank if own else 0, q_rank + kv_rank, rope_dim
+    p.wq, p.wkv, p.eps = wq.data_ptr(), _ptr(wkv), eps
+    if own and wkv.dtype != wq.dtype:
+        raise KernelError("latent_prep: the two norm weights must have one dtype")
+    if tables is not None and own:
+        cos, sin, rot = tables
+        p.cos_t, p.sin_t, p.table_rows, p.rot = cos.data_ptr(), sin.data_ptr(), cos.shape[0], rot
+    p.tok_pos, p.q_out, p.kv_out, p.err = tok_pos.data_ptr(), q_out.data_ptr(), _ptr(kv_out), err.data_ptr()
+    if append is not None and own:
+        a = append
+        p.append, p.tok_seq, p.seq_start, p.seq_len_before = 1, a["tok_seq"].data_ptr(), a["seq_start"].data_ptr(), a["seq_len_before"].data_ptr()
+        p.pool, p.page_table, p.table_stride = a["pool"].data_ptr(), a["page_table"].data_ptr(), a["page_table"].shape[1]
+        p.ring, p.pinned = a["ring"], a.get("pinned", 0)
+    f = _fn(load_module("latent.cu"), "llb_latent_prep", [_LatentPrepParams, c_int, c_int, c_int, c_void_p])
+    _check(f(p, _dt(proj), _dt(wq), T, _stream()), "latent attention (norms, key rotation, cache rows)")
+    return q_out, kv_out
+
+
+def latent_append(rows: torch.Tensor, tok_pos: torch.Tensor, append: dict) -> None:
+    """rows [T, width] into the tokens' rows of the paged cache (a pool of one key head of `width` elements)."""
+    _need_cuda(rows, tok_pos)
+    assert rows.is_contiguous()
+    a = append
+    f = _fn(load_module("latent.cu"), "llb_latent_append", [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
+                                                            c_void_p, c_void_p, c_int, c_int, c_int, c_void_p])
+    _check(f(_ptr(rows), _dt(rows), rows.shape[0], rows.shape[1], _ptr(tok_pos), _ptr(a["tok_seq"]), _ptr(a["seq_start"]),
+             _ptr(a["seq_len_before"]), _ptr(a["pool"]), _ptr(a["page_table"]), a["page_table"].shape[1], a["ring"],
+             a.get("pinned", 0), _stream()), "latent attention (cache append)")
+
+
+class _HeadMatmulParams(ctypes.Structure):
+    _fields_ = [("x", c_void_p), ("x_stride", c_int), ("x_head", c_int), ("m", c_void_p), ("y", c_void_p), ("y_stride", c_int),
+                ("y_head", c_int), ("T", c_int), ("H", c_int), ("n_in", c_int), ("n_out", c_int), ("tail", c_int), ("rot", c_int),
+                ("cos_t", c_void_p), ("sin_t", c_void_p), ("table_rows", c_int), ("tok_pos", c_void_p), ("gate", c_void_p),
+                ("gate_stride", c_int), ("err", c_void_p)]
+
+
+def head_matmul(x: torch.Tensor, m: torch.Tensor, *, tail: int = 0, tables=None, tok_pos=None, gate: Optional[torch.Tensor] = None,
+                err: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """y[t, h, :n_out] = x[t, h, :n_in] m[h] for x [T, H (n_in + tail)] and m [H, n_in, n_out], float32 accumulation; the
+    `tail` elements after a head's inputs follow its outputs in y [T, H (n_out + tail)], the first `rot` of them rotated in
+    pairs (2i, 2i+1) by tables = (cos, sin, rot) at the tokens' positions; with gate ([T, >= H] view) every head's
+    outputs are multiplied by sigmoid(gate[t, h])."""
+    _need_cuda(x, m, gate, tok_pos)
+    T = x.shape[0]
+    H, n_in, n_out = m.shape
+    assert x.stride(1) == 1 and m.is_contiguous() and m.dtype == x.dtype and x.shape[1] == H * (n_in + tail)
+    y = torch.empty((T, H * (n_out + tail)), dtype=x.dtype, device=x.device)
+    p = _HeadMatmulParams()
+    p.x, p.x_stride, p.x_head, p.m = x.data_ptr(), x.stride(0), n_in + tail, m.data_ptr()
+    p.y, p.y_stride, p.y_head = y.data_ptr(), y.stride(0), n_out + tail
+    p.T, p.H, p.n_in, p.n_out, p.tail = T, H, n_in, n_out, tail
+    if tail and tables is not None:
+        cos, sin, rot = tables
+        if tok_pos is None or err is None:
+            raise KernelError("head_matmul: a rotated tail needs the tokens' positions and an error word")
+        p.cos_t, p.sin_t, p.table_rows, p.rot, p.tok_pos, p.err = cos.data_ptr(), sin.data_ptr(), cos.shape[0], rot, tok_pos.data_ptr(), err.data_ptr()
+    if gate is not None:
+        assert gate.dtype == x.dtype and gate.stride(1) == 1
+        p.gate, p.gate_stride = gate.data_ptr(), gate.stride(0)
+    f = _fn(load_module("latent.cu"), "llb_head_matmul", [_HeadMatmulParams, c_int, c_void_p])
+    _check(f(p, _dt(x), _stream()), "per-head matrix product")
+    return y
+
+
+LATENT_MAX_ROW = 640          # the widest cache row (latent + rotated part) the attention kernel's key tile holds
+
+
+def require_latent_row(width: int, value_width: int) -> None:
+    if not (0 < value_width <= width <= LATENT_MAX_ROW):
+        raise KernelError(f"latent attention: cache rows of {width} elements ({value_width} of them the latent) are not supported "
+                          f"(at most {LATENT_MAX_ROW})")
+
+
+def latent_attention(decode: bool, q: torch.Tensor, nh: int, width: int, value_width: int, kv_new: Optional[torch.Tensor],
+                     pool: torch.Tensor, page_table: torch.Tensor, ring: int, pinned: int, seq_start: torch.Tensor,
+                     seq_len_before: torch.Tensor, n_seqs: int, max_new: int, window: Optional[int], scale: float,
+                     sink_logits: Optional[torch.Tensor], n_splits: int = 1) -> torch.Tensor:
+    """Softmax attention of nh query heads q [T, nh width] over one shared row per position: the key is the whole row
+    [width], the value its first `value_width` elements.  Rows of positions before the step come from the paged pool,
+    the step's own from kv_new [T, width] (None: from the pool too, where an earlier call has put them).  Causal, with
+    an optional window and a learned sink score per head (float32 [nh]) in the softmax's denominator.
+    Returns [T, nh value_width]."""
+    _need_cuda(q, kv_new, pool, page_table, sink_logits)
+    require_latent_row(width, value_width)
+    assert q.dtype == pool.dtype and q.stride(1) == 1 and (kv_new is None or (kv_new.dtype == q.dtype and kv_new.is_contiguous()))
+    assert sink_logits is None or (sink_logits.dtype == torch.float32 and sink_logits.numel() == nh)
+    out = torch.empty((q.shape[0], nh * value_width), dtype=q.dtype, device=q.device)
+    p = _AttnParams()
+    p.q, p.row_stride, p.out = q.data_ptr(), q.stride(0), out.data_ptr()
+    if kv_new is not None:
+        p.k_new, p.kv_row_stride = kv_new.data_ptr(), kv_new.stride(0)
+    p.kpool, p.page_table, p.table_stride, p.ring, p.pinned = pool.data_ptr(), page_table.data_ptr(), page_table.shape[1], ring, pinned
+    p.seq_start, p.seq_len_before = seq_start.data_ptr(), seq_len_before.data_ptr()
+    p.nh, p.nkvh, p.window, p.scale = nh, 1, int(window or 0), scale
+    p.all_from_cache = int(kv_new is None)
+    p.sink_logits, p.v_in_k, p.n_splits = _ptr(sink_logits), 1, 1
+    lib = _attn_lib(width, value_width) if width <= 256 else load_module("attention_simt.cu", {"LLB_HEAD_DIM": width, "LLB_VALUE_DIM": value_width})
+    if not decode:
+        f = _fn(lib, "llb_attn_prefill", [_AttnParams, c_int, c_int, c_int, c_void_p])
+        _check(f(p, _dt(q), n_seqs, max_new, _stream()), "latent attention (prefill)")
+        return out
+    keep = None
+    p.n_splits = n_splits
+    if n_splits > 1:
+        part_o = torch.empty((n_seqs, nh, n_splits, value_width), dtype=torch.float32, device=q.device)
+        part_ml = torch.empty((n_seqs, nh, n_splits, 2), dtype=torch.float32, device=q.device)
+        p.part_o, p.part_ml = part_o.data_ptr(), part_ml.data_ptr()
+        keep = (part_o, part_ml)
+    f = _fn(lib, "llb_attn_decode", [_AttnParams, c_int, c_int, c_void_p])
+    _check(f(p, _dt(q), n_seqs, _stream()), "latent attention (decode)", 2 if n_splits > 1 else 1)
+    del keep
+    return out

@@ -256,6 +256,41 @@ def swiglu(gate_up: torch.Tensor) -> torch.Tensor:
     return out
 
 
+GLU_ACTS = {"silu": 0, "relu": 1, "gelu_tanh": 2}
+
+
+def glu(gate_up: torch.Tensor, act: str, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+    """[T, 2I] (gate columns first) -> [T, I]: act(gate) * up with act "silu", "relu" or "gelu_tanh", in float32 with
+    one rounding at the output."""
+    _need_cuda(gate_up)
+    assert gate_up.is_contiguous()
+    T, I2 = gate_up.shape
+    out = torch.empty((T, I2 // 2), dtype=out_dtype or gate_up.dtype, device=gate_up.device)
+    f = _fn(_lib_basic(), "llb_glu", [c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_void_p])
+    _check(f(_ptr(out), _dt(out), _ptr(gate_up), _dt(gate_up), T, I2 // 2, GLU_ACTS[act], _stream()), f"gated activation ({act})")
+    return out
+
+
+def scaled_norm_add(residual: torch.Tensor, delta: Optional[torch.Tensor], w_post: Optional[torch.Tensor], mult: float,
+                    w_next: Optional[torch.Tensor], eps: float, offset: float, out_dtype: Optional[torch.dtype] = None):
+    """residual (float32 [T, H]) += mult * delta / sqrt(mean(delta^2) + eps) * (w_post + offset); with w_next also returns
+    residual / sqrt(mean(residual^2) + eps) * (w_next + offset) of the new rows, from the same pass.  Without delta
+    only the second half (a plain norm of the stream)."""
+    _need_cuda(residual, delta, w_post, w_next)
+    assert residual.dtype == torch.float32 and residual.is_contiguous()
+    T, H = residual.shape
+    if delta is not None:
+        assert delta.shape == residual.shape and delta.is_contiguous() and w_post is not None
+    w = w_post if w_post is not None else w_next
+    assert w is not None and (w_next is None or w_post is None or w_next.dtype == w_post.dtype)
+    out = torch.empty((T, H), dtype=out_dtype, device=residual.device) if w_next is not None else None
+    f = _fn(_lib_basic(), "llb_scaled_norm_add", [c_void_p, c_void_p, c_int, c_void_p, c_float, c_void_p, c_int, c_void_p, c_int,
+                                                  c_int, c_int, c_float, c_float, c_void_p])
+    _check(f(_ptr(residual), _ptr(delta), _dt(delta) if delta is not None else 0, _ptr(w_post), mult, _ptr(w_next), _dt(w),
+             _ptr(out), DT[out_dtype] if out is not None else 0, T, H, eps, offset, _stream()), "normed output into the stream")
+    return out
+
+
 def dense_binary(out: torch.Tensor, a: torch.Tensor, b: torch.Tensor, op: str):
     """out = a + b (op "add") or out = b * a / (1 + exp(-a)) (op "swiglu": a the gate, b the up
     projection) on contiguous tensors of one dtype and one shape."""
@@ -581,7 +616,8 @@ class _AttnParams(ctypes.Structure):
                 ("table_stride", c_int), ("ring", c_int), ("seq_start", c_void_p),
                 ("seq_len_before", c_void_p), ("nh", c_int), ("nkvh", c_int), ("window", c_int),
                 ("scale", c_float), ("all_from_cache", c_int), ("n_splits", c_int), ("part_o", c_void_p), ("part_ml", c_void_p),
-                ("keep_first", c_int), ("pinned", c_int), ("sink", c_int)]
+                ("keep_first", c_int), ("pinned", c_int), ("sink", c_int),
+                ("sink_logits", c_void_p), ("v_in_k", c_int), ("kv_row_stride", c_int)]
 
 
 class _MmaAttnParams(ctypes.Structure):

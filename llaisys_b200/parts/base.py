@@ -70,11 +70,14 @@ class TensorDecl:
     use: "matrix" for an operand of a matrix product or a table of rows (kept in the model's
     dtype, whatever the file stores, so that it can feed the tensor cores), "vector" for what
     enters 32-bit arithmetic only (a norm's weight, a bias: under a bfloat16 model such a tensor
-    stays float32 if the file stores it in 32 bits)."""
+    stays float32 if the file stores it in 32 bits).  free: axes whose size no configuration key gives: the file's
+    size is accepted there and the part reads it from the tensor it receives (`shape` holds the size that the
+    random-weights mode uses)."""
     shape: Tuple[int, ...]
     kind: str = "float"
     init: str = "normal"
     use: str = "matrix"
+    free: Tuple[int, ...] = ()
 
 
 @dataclass(frozen=True)
@@ -114,6 +117,12 @@ class Norm(Part):
                 rows: Optional[torch.Tensor] = None) -> torch.Tensor:
         """residual (float32 [T, H]) += delta (if given), then the normalised rows in the
         activation dtype.  With `rows` only those rows, and the residual is not written."""
+        raise NotImplementedError
+
+    def forward_scaled_add(self, residual: torch.Tensor, delta: torch.Tensor, mult: float, then: "Optional[Norm]" = None):
+        """residual (float32 [T, H]) += mult * norm(delta): the norm of a part's output on its way into the stream.
+        With `then` (a norm of the same kind) also returns then's normalised rows of the new stream, from the same
+        pass; otherwise None."""
         raise NotImplementedError
 
 
@@ -171,17 +180,20 @@ class FeedForward(Part):
 
 @dataclass
 class SubLayer:
-    """A built sub-layer: the part, its category ("mixer" or "ffn") and the norm before it (or None)."""
+    """A built sub-layer: the part, its category ("mixer" or "ffn"), the norm before it (or None) and, in arrangements
+    that have one, the norm of its output."""
     category: str
     part: Part
     norm: Optional[Norm]
+    post_norm: Optional[Norm] = None
 
 
 class Block(Part):
     """Arrangement of one layer.  Built with the layer's sub-layers instead of a PartSpec."""
 
-    def __init__(self, sublayers, env: BuildEnv):
+    def __init__(self, sublayers, env: BuildEnv, params=None):
         self.sublayers, self.env = list(sublayers), env
+        self.params = dict(params or {})
         self.spec = None
 
     def forward(self, residual: torch.Tensor, pending: Optional[torch.Tensor], ctx, users):

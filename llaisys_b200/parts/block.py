@@ -15,6 +15,8 @@ class PreNormResidual(Block):
 
     def forward(self, residual, pending, ctx, users):
         from .. import kernels
+        if isinstance(pending, PendingNormed):
+            pending = settle(residual, pending)
         mixers = iter(users)
         for sub in self.sublayers:
             if sub.norm is not None:
@@ -41,6 +43,8 @@ class ParallelResidual(Block):
 
     def forward(self, residual, pending, ctx, users):
         from .. import kernels
+        if isinstance(pending, PendingNormed):
+            pending = settle(residual, pending)
         if pending is not None:
             kernels.residual_add(residual, pending)
         norms = [sub.norm for sub in self.sublayers]
@@ -58,3 +62,62 @@ class ParallelResidual(Block):
             elif not sub.part.forward_into(h, ctx, residual):
                 kernels.residual_add(residual, sub.part.forward(h, ctx))
         return residual, None
+
+
+@register_part("block", "sandwich_residual")
+class SandwichResidual(Block):
+    """x -> x + mult * post_norm(part(norm(x))) for every sub-layer in turn: each part sits between a norm of its input
+    and a norm of its output, and the normed output is scaled by the layer's constant `mult` before it joins the float32
+    stream.  Output norm, add and the next sub-layer's input norm are one pass over the row (Norm.forward_scaled_add);
+    the layer's last part leaves its output pending with its norm, and the block after it (or the final norm) runs
+    that pass, so a layer costs one norm launch per part.  params: mult."""
+    capturable = True
+
+    def __init__(self, sublayers, env, params=None):
+        super().__init__(sublayers, env, params)
+        self.mult = float(self.params.get("mult", 1.0))
+        for sub in self.sublayers:
+            if sub.norm is None or sub.post_norm is None:
+                raise ValueError("every sub-layer of this arrangement has a norm before and a norm after its part")
+
+    def forward(self, residual, pending, ctx, users):
+        mixers = iter(users)
+        h = None
+        for i, sub in enumerate(self.sublayers):
+            if i == 0:
+                h = settle(residual, pending, sub.norm)
+            if sub.category == "mixer":
+                delta = sub.part.forward(h, ctx, next(mixers))
+            else:
+                delta = sub.part.forward(h, ctx)
+            if i + 1 < len(self.sublayers):
+                h = sub.post_norm.forward_scaled_add(residual, delta, self.mult, then=self.sublayers[i + 1].norm)
+            else:
+                pending = PendingNormed(delta, sub.post_norm, self.mult)
+        return residual, pending
+
+
+class PendingNormed:
+    """A part's output that has not joined the stream yet: it is to be normed by `norm`, scaled by `mult` and added."""
+
+    def __init__(self, delta, norm, mult):
+        self.delta, self.norm, self.mult = delta, norm, mult
+
+
+def settle(residual, pending, norm=None, rows=None):
+    """Adds whatever the block before left pending to the float32 stream and returns `norm` of the result (None without
+    a norm).  With `rows` only those rows are returned (the stream itself is still brought up to date)."""
+    from .. import kernels
+    if isinstance(pending, PendingNormed):
+        if rows is None:
+            try:
+                return pending.norm.forward_scaled_add(residual, pending.delta, pending.mult, then=norm)
+            except ValueError:
+                pass                                    # norms of different kinds: two passes
+        pending.norm.forward_scaled_add(residual, pending.delta, pending.mult)
+        pending = None
+    if norm is None:
+        if pending is not None:
+            kernels.residual_add(residual, pending)
+        return None
+    return norm.forward(residual, pending, rows=rows)

@@ -1,0 +1,132 @@
+from __future__ import annotations
+
+import torch
+
+from .. import kernels
+from .attention import decode_splits
+from .base import KVNeed, Mixer, TensorDecl, build_part, register_part
+
+
+@register_part("mixer", "latent_attention")
+class LatentAttention(Mixer):
+    """Causal softmax attention whose queries, keys and values pass through low-rank latents; a token leaves one row
+    [c (kv_rank) | rotated shared key part (rope_dim)] in the cache for all heads together.
+
+        cq = rms_norm(Wdq h; w)                  q[h] = Wuq[h] cq = [q_n (nope_dim) | q_r (rope_dim)], q_r rotated
+        [c' | k_r] = Wdkv h                      c = rms_norm(c'; w), k_r rotated (one for all heads)
+        k_n[h] = Wuk[h] c,  v[h] = Wuv[h] c
+        score(i, j) = (q_n[h]_i . k_n[h]_j + q_r[h]_i . k_r_j) * scale      for j <= i (and i - j < window)
+        weights = softmax over the visible j, with one more term e^(sink[h]) in the denominator that carries no value
+        out = Wo concat_h(sigmoid(Wg h)_h * sum_j weight_j v[h]_j)
+
+    The up projections of keys and values never run over the cache: q_n . (Wuk[h] c) = (Wuk[h]^T q_n) . c and
+    sum_j w_j Wuv[h] c_j = Wuv[h] sum_j w_j c_j, so the heads' queries are carried into the latent space (a per-head
+    product), attention runs over the cached rows as one key/value head shared by all query heads (key: the whole row,
+    value: its first kv_rank elements), and the latent result is carried into each head's value space.  Scores,
+    softmax and all norms are float32.
+
+    `own_kv` false: the layer has no Wdkv and reads the rows another layer cached (the run order's `cache_of`), with
+    its own up projections, queries, window and everything else.
+
+    Cache: one key head of kv_rank + rope_dim elements, no value pool.  `cache_window` None keeps every row (needed
+    when other layers read the cache; the window is then a mask only), otherwise a ring of pages for the window: a step
+    of several tokens then attends over the cache and the step's own rows and appends afterwards; single tokens, and
+    caches that keep every row, append first.
+
+    params: hidden_size, num_heads, nope_dim, rope_dim, value_dim, q_rank, kv_rank, scale, window, eps, sink, head_gate,
+    own_kv, cache_window, position (PartSpec of a position encoding with pair_tables()), names.
+    """
+    capturable = True
+
+    def __init__(self, spec, env):
+        super().__init__(spec, env)
+        p = spec.params
+        self.hidden, self.nh = int(p["hidden_size"]), int(p["num_heads"])
+        self.dn, self.dr, self.dv = int(p["nope_dim"]), int(p["rope_dim"]), int(p["value_dim"])
+        self.q_rank, self.kv_rank = int(p["q_rank"]), int(p["kv_rank"])
+        self.scale, self.eps = float(p["scale"]), float(p["eps"])
+        self.window = int(p["window"]) if p.get("window") is not None else None
+        if self.window is not None and self.window <= 0:
+            raise ValueError(f"a window holds at least one key, got {self.window}")
+        self.sink, self.head_gate = bool(p.get("sink", False)), bool(p.get("head_gate", False))
+        self.own_kv = bool(p.get("own_kv", True))
+        self.cache_window = p.get("cache_window")
+        if self.cache_window is not None and (self.window is None or self.cache_window < self.window):
+            raise ValueError("the cache must keep at least the keys the window shows")
+        self.row = self.kv_rank + self.dr
+        kernels.require_latent_row(self.row, self.kv_rank)
+        self.position = build_part("position", p["position"], env) if p.get("position") else None
+        if self.position is not None and not hasattr(self.position, "pair_tables"):
+            raise ValueError("this mixer takes a position encoding that hands out pair_tables()")
+        self.names = dict({"dq": "dq", "dq_norm": "dq.norm", "uq": "uq", "dkv": "dkv", "dkv_norm": "dkv.norm", "uk": "uk",
+                           "uv": "uv", "sink": "sink", "g": "g", "o": "o"}, **(p.get("names") or {}))
+        self.w_in = self.w_uq = self.w_uk = self.w_uv_t = self.w_o = self.w_qn = self.w_kvn = self.sink_logits = None
+
+    def prepare(self, max_positions):
+        if self.position is not None:
+            self.position.prepare(max_positions)
+
+    def kv_need(self):
+        return KVNeed(1, self.row, 0, self.cache_window)
+
+    def tensors(self):
+        n, D, H = self.names, self.hidden, self.nh
+        t = {n["dq"]: TensorDecl((self.q_rank, D)), n["dq_norm"]: TensorDecl((self.q_rank,), init="one_plus_normal", use="vector"),
+             n["uq"]: TensorDecl((H * (self.dn + self.dr), self.q_rank)), n["uk"]: TensorDecl((H * self.dn, self.kv_rank)),
+             n["uv"]: TensorDecl((H * self.dv, self.kv_rank)), n["o"]: TensorDecl((D, H * self.dv))}
+        if self.own_kv:
+            t[n["dkv"]] = TensorDecl((self.row, D))
+            t[n["dkv_norm"]] = TensorDecl((self.kv_rank,), init="one_plus_normal", use="vector")
+        if self.sink:
+            t[n["sink"]] = TensorDecl((H,), use="vector")
+        if self.head_gate:
+            t[n["g"]] = TensorDecl((H, D))
+        return t
+
+    def load(self, tensors):
+        n, H = self.names, self.nh
+        ts = [tensors[n["dq"]]] + ([tensors[n["dkv"]]] if self.own_kv else []) + ([tensors[n["g"]]] if self.head_gate else [])
+        dt = ts[0].dtype
+        for t in ts[1:]:
+            dt = torch.promote_types(dt, t.dtype)
+        self.w_in = torch.cat([t.to(dt) for t in ts], dim=0).contiguous()       # [query latent | kv latent, key part | gates]
+        self.gate_off = self.q_rank + (self.row if self.own_kv else 0)
+        self.w_uq = tensors[n["uq"]].contiguous()
+        self.w_uk = tensors[n["uk"]].reshape(H, self.dn, self.kv_rank).contiguous()                 # [h, nope, latent]
+        self.w_uv_t = tensors[n["uv"]].reshape(H, self.dv, self.kv_rank).transpose(1, 2).contiguous()   # [h, latent, value]
+        self.w_o = tensors[n["o"]].contiguous()
+        self.w_qn = tensors[n["dq_norm"]].float().contiguous()
+        self.w_kvn = tensors[n["dkv_norm"]].float().contiguous() if self.own_kv else None
+        self.sink_logits = tensors[n["sink"]].float().contiguous() if self.sink else None
+
+    def _splits(self, ctx) -> int:
+        from ..cache.kv import ring_pages
+        splits = decode_splits(ctx, 1)
+        if self.window is not None:
+            splits = min(splits, ring_pages(self.window))
+        return max(1, min(splits, 64))
+
+    def forward(self, x, ctx, call):
+        kv = ctx.kv(call)
+        if kv.writable != self.own_kv:
+            raise ValueError("a layer with its own latent projection keeps its own cache; one without reads another layer's")
+        proj = kernels.linear(x, self.w_in)
+        tables = self.position.pair_tables(ctx.max_position + 1) if self.position is not None else None
+        append = None
+        if kv.writable:
+            append = dict(tok_seq=ctx.tok_seq, seq_start=ctx.seq_start, seq_len_before=ctx.seq_len_before, pool=kv.k,
+                          page_table=kv.page_table, ring=kv.ring, pinned=kv.pinned)
+        ring_cache = kv.writable and self.cache_window is not None
+        after = ring_cache and not ctx.is_decode          # a ring is appended to after a step of several tokens
+        cq, rows = kernels.latent_prep(proj, self.q_rank, self.kv_rank, self.dr, self.w_qn, self.w_kvn, self.eps, tables,
+                                       ctx.tok_pos, ctx.err, append=None if after else append)
+        q = kernels.linear(cq, self.w_uq)
+        q_lat = kernels.head_matmul(q, self.w_uk, tail=self.dr, tables=tables, tok_pos=ctx.tok_pos, err=ctx.err)
+        o_lat = kernels.latent_attention(ctx.is_decode, q_lat, self.nh, self.row, self.kv_rank, rows if after else None, kv.k,
+                                         kv.page_table, kv.ring, kv.pinned, ctx.seq_start, ctx.seq_len_before, ctx.n_seqs,
+                                         ctx.max_new, self.window, self.scale, self.sink_logits,
+                                         n_splits=self._splits(ctx) if ctx.is_decode else 1)
+        if after:
+            kernels.latent_append(rows, ctx.tok_pos, append)
+        heads = kernels.head_matmul(o_lat, self.w_uv_t, gate=proj[:, self.gate_off:] if self.head_gate else None)
+        return kernels.linear(heads, self.w_o, out_dtype=torch.float32)

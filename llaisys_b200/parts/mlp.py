@@ -47,3 +47,39 @@ class SwiGLUMLP(FeedForward):
             kernels.residual_add(residual, kernels.linear(act, self.down))
             return True
         return False
+
+
+@register_part("ffn", "gated_mlp")
+class GatedMLP(FeedForward):
+    """down(act(gate(x)) * up(x)), no biases, with the activation a parameter: "silu", "relu" or "gelu_tanh".  The gate
+    and up matrices are kept as one [2I, H] matrix so that one product serves both; the activation and the product of
+    the halves are one pass in float32.  The result is returned in float32 (it may be normed before it joins the
+    stream).  params: hidden_size, intermediate_size, act, names (local tensor names of gate, up, down)."""
+    capturable = True
+
+    def __init__(self, spec, env):
+        super().__init__(spec, env)
+        p = spec.params
+        self.hidden, self.inter, self.act = int(p["hidden_size"]), int(p["intermediate_size"]), str(p.get("act", "silu"))
+        if self.act not in kernels.ops.GLU_ACTS:
+            raise ValueError(f"unknown activation {self.act!r}; known: {sorted(kernels.ops.GLU_ACTS)}")
+        self.names = dict({"gate": "gate_proj.weight", "up": "up_proj.weight", "down": "down_proj.weight"}, **(p.get("names") or {}))
+        self.gate_up = self.down = None
+
+    def tensors(self):
+        n = self.names
+        return {n["gate"]: TensorDecl((self.inter, self.hidden)), n["up"]: TensorDecl((self.inter, self.hidden)),
+                n["down"]: TensorDecl((self.hidden, self.inter))}
+
+    def load(self, tensors):
+        g, u = tensors[self.names["gate"]], tensors[self.names["up"]]
+        dt = torch.promote_types(g.dtype, u.dtype)
+        self.gate_up = torch.cat([g.to(dt), u.to(dt)], dim=0).contiguous()
+        self.down = tensors[self.names["down"]].contiguous()
+
+    def forward(self, x, ctx):
+        if self.act == "silu":
+            act = kernels.linear_swiglu(x, self.gate_up)
+        else:
+            act = kernels.glu(kernels.linear(x, self.gate_up), self.act)
+        return kernels.linear(act, self.down, out_dtype=torch.float32)

@@ -121,3 +121,74 @@ class RotaryLeading(PositionEncoding):
         if t is not None:
             kernels.rope_lead_append(qkv, num_heads, num_kv_heads, self.head_dim, self.head_dim, self.dims, cos=t[0], sin=t[1],
                                      tok_pos=ctx.tok_pos, err=ctx.err)
+
+
+def yarn_frequencies(dims: int, base: float, yarn):
+    """float64 frequencies [dims / 2] of a rotation with the wavelength-dependent rescaling known as YaRN, and the factor
+    both cos and sin are multiplied by.  yarn = {factor, original, fast, slow}: with d(r) = dims ln(original / (2 pi r)) /
+    (2 ln base) the dimension whose wavelength makes r turns over `original` positions, lo = max(floor(d(fast)), 0),
+    hi = min(ceil(d(slow)), dims - 1) and ramp_i = clamp((i - lo) / max(hi - lo, 0.001), 0, 1), the frequency is
+    f_i / factor * ramp_i + f_i (1 - ramp_i) (slow dimensions are stretched, fast ones kept) and the magnitude
+    0.1 ln(factor) + 1.  None: plain frequencies base^(-2i/dims), magnitude 1."""
+    import math
+    i = torch.arange(dims // 2, dtype=torch.float64)
+    f = torch.pow(torch.tensor(base, dtype=torch.float64), -2.0 * i / dims)
+    if not yarn:
+        return f, 1.0
+    factor, original = float(yarn["factor"]), float(yarn["original"])
+
+    def turn_dim(turns: float) -> float:
+        return dims * math.log(original / (2.0 * math.pi * turns)) / (2.0 * math.log(base))
+
+    lo = max(math.floor(turn_dim(float(yarn["fast"]))), 0)
+    hi = min(math.ceil(turn_dim(float(yarn["slow"]))), dims - 1)
+    ramp = torch.clamp((i - lo) / max(hi - lo, 0.001), 0.0, 1.0)
+    return f / factor * ramp + f * (1.0 - ramp), 0.1 * math.log(factor) + 1.0
+
+
+@register_part("position", "rope_interleaved")
+class RotaryInterleaved(PositionEncoding):
+    """Rotary encoding of neighbouring pairs: of a vector of `width` elements the pairs (2i, 2i+1), i < dims / 2, are
+    rotated by the angle p * f_i at position p, (u, v) -> (u cos - v sin, v cos + u sin); the elements from `dims` on
+    pass unchanged.  Frequencies and magnitude come from yarn_frequencies().  The part hands out float32 tables
+    [positions, dims / 2] of cos and sin (magnitude included), built in float64 on the host and sized once by
+    prepare(); the mixers' kernels apply them.  params: width, dims, base, yarn (dict or None)."""
+    capturable = True
+
+    def __init__(self, spec, env):
+        super().__init__(spec, env)
+        p = spec.params
+        self.width, self.dims, self.base = int(p["width"]), int(p["dims"]), float(p["base"])
+        self.yarn = dict(p["yarn"]) if p.get("yarn") else None
+        if self.dims % 2 or not (0 <= self.dims <= self.width):
+            raise ValueError(f"rotated dimensions must be even and at most {self.width}, got {self.dims}")
+        self._tables = None
+        self._prepared = False
+
+    def pair_tables(self, positions: int):
+        """(cos, sin, dims), the tables float32 [rows >= positions, dims / 2]; None when nothing is rotated."""
+        if self.dims == 0:
+            return None
+        if self._tables is None or self._tables[0].shape[0] < positions:
+            if self._prepared:
+                raise ValueError(f"position {positions - 1} lies beyond the {self._tables[0].shape[0]} positions the "
+                                 f"rotary table was prepared for")
+            rows = max(positions, 2 * (self._tables[0].shape[0] if self._tables is not None else 0))
+            key = ("pairs", self.dims, self.base, tuple(sorted(self.yarn.items())) if self.yarn else None, str(self.env.device))
+            have = _TABLES.get(key)
+            if have is None or have[0].shape[0] < rows:
+                f, mag = yarn_frequencies(self.dims, self.base, self.yarn)
+                ang = torch.arange(rows, dtype=torch.float64)[:, None] * f[None, :]
+                have = ((torch.cos(ang) * mag).to(torch.float32).to(self.env.device).contiguous(),
+                        (torch.sin(ang) * mag).to(torch.float32).to(self.env.device).contiguous())
+                _TABLES[key] = have
+            self._tables = have
+        return self._tables[0], self._tables[1], self.dims
+
+    def prepare(self, max_positions):
+        self._prepared = False
+        self.pair_tables(max_positions)
+        self._prepared = True
+
+    def apply(self, qkv, num_heads, num_kv_heads, ctx):
+        raise NotImplementedError("this encoding hands out pair_tables(); the mixers that take it rotate in their own kernels")

@@ -130,7 +130,8 @@ def check_tensors(model, source) -> None:
         if n not in have:
             continue
         stored, shape = have[n]
-        if tuple(shape) != tuple(decl.shape):
+        free = getattr(decl, "free", ())
+        if len(shape) != len(decl.shape) or any(a != b for i, (a, b) in enumerate(zip(shape, decl.shape)) if i not in free):
             wrong_shape[n] = (tuple(shape), tuple(decl.shape))
         if (decl.kind == "float" and stored not in _FLOAT) or (decl.kind == "int" and stored not in _INT):
             wrong_kind[n] = (stored, "floating-point" if decl.kind == "float" else "integer")
