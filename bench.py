@@ -517,9 +517,50 @@ def design_configs(size: str, layers: int):
     return vz, qw
 
 
+# ---- `--design nubedra`: the Nubedra design (recurrent and latent-attention layers between two norms, dense gated
+# feed-forward) beside the Qwen2 dense decoder at equal width, heads, head size and feed-forward width
+# width, heads, unrotated / rotated query-key dims, value dims, query latent, key/value latent, window, ff,
+# recurrent heads, their key channels, their value channels, kv heads of the Qwen2 model beside it
+NUBEDRA_SIZES = {
+    "a": (1536, 12, 96, 32, 128, 768, 192, 1024, 4096, 12, 64, 128, 2),
+    "b": (2048, 16, 96, 32, 128, 1024, 224, 2048, 5632, 16, 64, 128, 4),
+    "c": (4096, 32, 64, 64, 128, 1536, 512, 4096, 11008, 32, 128, 128, 8),
+}
+
+
+def nubedra_configs(size: str, layers: int):
+    """(Nubedra config, Qwen2 config) of one size.  Layers in turn: a recurrent one, a latent-attention one whose cache the
+    next one reads, that reader, a latent-attention one with a ring of its own; every layer has a feed-forward."""
+    D, H, dn, dr, dv, qr, kvr, window, ff, gh, gk, gv, G = NUBEDRA_SIZES[size]
+    vocab = 32768
+
+    def latent(kv_from=None):
+        m = {"heads": H, "dim": dn, "rot_dim": dr, "vdim": dv, "q_rank": qr, "kv_rank": kvr, "scale": (dn + dr) ** -0.5,
+             "mask": {"size": window}, "rot": {"dims": dr, "base": 1000000.0,
+                                               "scaling": {"factor": 4.0, "original": 4096, "fast": 32.0, "slow": 1.0}}}
+        if kv_from is not None:
+            m["kv_from"] = kv_from
+        return {"type": "latent_attention", "mixer": m, "mlp": {"kind": "dense", "ff": ff}}
+
+    nb_layers = []
+    for i in range(layers):
+        if i % 4 == 0:
+            nb_layers.append({"type": "gla", "mixer": {"heads": gh, "dim": gk, "vdim": gv, "tau": 16.0}, "mlp": {"kind": "dense", "ff": ff}})
+        else:
+            nb_layers.append(latent(i - 1 if i % 4 == 2 else None))
+    nb = {"architecture": "Nubedra", "vocab": vocab, "width": D, "norm": {"eps": 1e-6}, "embedding": {"scale": 1.0},
+          "residual_mult": 0.5, "layers": nb_layers}
+    qw = dict(QWEN2_1_5B, num_hidden_layers=layers, hidden_size=D, num_attention_heads=H, num_key_value_heads=G, head_dim=dn + dr,
+              intermediate_size=ff, vocab_size=vocab, use_sliding_window=False)
+    return nb, qw
+
+
+DESIGNS = {"vumezen": (DESIGN_SIZES, design_configs), "nubedra": (NUBEDRA_SIZES, nubedra_configs)}
+
+
 def design_run(args) -> int:
     """Prefill (one step over --tokens tokens) and decode (--batch sequences that hold --tokens tokens each) of the
-    Vumezen design and of the Qwen2 dense decoder at equal layer sizes: time per step, tokens a second, and each kernel's
+    chosen design and of the Qwen2 dense decoder at equal layer sizes: time per step, tokens a second, and each kernel's
     share of a step (torch.profiler).  One JSON line per model and phase.  Inputs: the weights of either model are
     larger than L2, and nothing is flushed between steps."""
     import collections
@@ -539,8 +580,9 @@ def design_run(args) -> int:
     torch.cuda.set_device(dev)
     layers = args.layers or 8
     T, B = args.tokens, max(1, args.batch)
-    for size in (args.size.split(",") if args.size else sorted(DESIGN_SIZES)):
-        for name, cfg_dict in zip(("vumezen", "qwen2"), design_configs(size, layers)):
+    sizes, configs = DESIGNS[args.design]
+    for size in (args.size.split(",") if args.size else sorted(sizes)):
+        for name, cfg_dict in zip((args.design, "qwen2"), configs(size, layers)):
             cfg = config_from_dict(cfg_dict)
             model = DecoderModel(cfg.to_spec(), BuildEnv(torch.bfloat16, dev))
             load_weights(model, RandomSource(model.expected_tensors(), seed=0, dtype=torch.bfloat16, device=dev))
@@ -752,7 +794,7 @@ def main() -> int:
                          "of the prefill's products alone at --tokens tokens; builds that kernel with -DLLB_STAMPS=1")
     ap.add_argument("--timeline", choices=["decode", "prefill"], default=None,
                     help="print the per-kernel timeline of a step (torch.profiler, no ncu) instead of measuring")
-    ap.add_argument("--design", choices=["vumezen"], default=None,
+    ap.add_argument("--design", choices=sorted(DESIGNS), default=None,
                     help="measure this design beside the Qwen2 dense decoder at equal layer sizes (prefill of --tokens tokens, "
                          "decode at --batch) instead of the benchmark; --size picks among the sizes (default: all)")
     ap.add_argument("--size", default=None, help="with --design: comma-separated sizes of " + ", ".join(sorted(DESIGN_SIZES)))

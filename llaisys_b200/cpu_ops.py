@@ -95,12 +95,13 @@ def route_top(logits: np.ndarray, bias, top: int, scale: float):
 
 
 def self_attention(q: np.ndarray, k: np.ndarray, v: np.ndarray, scale: float, window=None, keep_first: int = 0,
-                   sink: bool = False) -> np.ndarray:
+                   sink: bool = False, sink_logits=None) -> np.ndarray:
     """Causal grouped-query attention of q [qlen, nh, d] over k [kvlen, nkvh, d], v [kvlen, nkvh, dv], the queries being
     the last qlen of the kvlen positions: query i sees keys t <= kvlen - qlen + i; head h reads kv head
     h // (nh / nkvh); softmax with the maximum subtracted (src/ops/self_attention/cpu/self_attention_cpu.cpp:28-112).
     Not in that project: window (a query at position p sees only the keys p - window < t <= p), keep_first (the keys
-    t < keep_first stay visible behind the window) and sink (one more term e^0 in the denominator, without a value)."""
+    t < keep_first stay visible behind the window), sink (one more term e^0 in the denominator, without a value) and
+    sink_logits [nh] (that term is e^sink_logits[h] instead)."""
     qlen, nh, d = q.shape
     kvlen, nkvh, dv = v.shape
     group = nh // nkvh
@@ -115,10 +116,11 @@ def self_attention(q: np.ndarray, k: np.ndarray, v: np.ndarray, scale: float, wi
         s = (q[:, h, :] @ k[:, h // group, :].T) * np.float32(scale)
         s = np.where(visible, s, -np.inf)
         m = s.max(axis=-1, keepdims=True)
-        if sink:
-            m = np.maximum(m, np.float32(0))
+        s0 = np.float32(sink_logits[h]) if sink_logits is not None else np.float32(0)
+        if sink or sink_logits is not None:
+            m = np.maximum(m, s0)
         e = np.where(visible, np.exp(s - m), 0.0).astype(np.float32)
-        den = e.sum(axis=-1, keepdims=True) + (np.exp(-m).astype(np.float32) if sink else np.float32(0))
+        den = e.sum(axis=-1, keepdims=True) + (np.exp(s0 - m).astype(np.float32) if (sink or sink_logits is not None) else np.float32(0))
         out[:, h, :] = (e / den) @ v[:, h // group, :]
     return out
 
@@ -127,3 +129,57 @@ def swiglu(gate: np.ndarray, up: np.ndarray) -> np.ndarray:
     """out = up * gate / (1 + exp(-gate)) (src/ops/swiglu/cpu/swiglu_cpu.cpp:13-21)."""
     g, u = gate.astype(np.float32), up.astype(np.float32)
     return u * (g / (np.float32(1.0) + np.exp(-g)))
+
+
+def rope_pairs(x: np.ndarray, pos_ids: np.ndarray, dims: int, base: float, yarn=None) -> np.ndarray:
+    """Rotation of the neighbouring pairs (2i, 2i+1), i < dims/2, of the last axis of x [seq, heads, d] by the angle
+    p * f_i; the other dimensions pass.  f_i = base^(-2i/dims), or with yarn = {factor, original, fast, slow} the
+    rescaled frequencies and magnitude of parts/rope.py: yarn_frequencies (not in xsmccc/llaisys)."""
+    import math
+    x = x.astype(np.float32).copy()
+    half = dims // 2
+    if half == 0:
+        return x
+    i = np.arange(half, dtype=np.float64)
+    f = np.power(float(base), -2.0 * i / dims)
+    mag = 1.0
+    if yarn:
+        def turn_dim(turns):
+            return dims * math.log(float(yarn["original"]) / (2.0 * math.pi * turns)) / (2.0 * math.log(float(base)))
+        lo, hi = max(math.floor(turn_dim(float(yarn["fast"]))), 0), min(math.ceil(turn_dim(float(yarn["slow"]))), dims - 1)
+        ramp = np.clip((i - lo) / max(hi - lo, 0.001), 0.0, 1.0)
+        f = f / float(yarn["factor"]) * ramp + f * (1.0 - ramp)
+        mag = 0.1 * math.log(float(yarn["factor"])) + 1.0
+    ang = np.asarray(pos_ids, dtype=np.float64)[:, None] * f[None, :]
+    cos, sin = (np.cos(ang) * mag)[:, None, :].astype(np.float32), (np.sin(ang) * mag)[:, None, :].astype(np.float32)
+    u, v = x[..., 0:dims:2].copy(), x[..., 1:dims:2].copy()
+    x[..., 0:dims:2] = u * cos - v * sin
+    x[..., 1:dims:2] = v * cos + u * sin
+    return x
+
+
+def glu(gate: np.ndarray, up: np.ndarray, act: str) -> np.ndarray:
+    """act(gate) * up with act "silu", "relu" or "gelu_tanh" (not in xsmccc/llaisys beyond swiglu)."""
+    g, u = gate.astype(np.float32), up.astype(np.float32)
+    if act == "relu":
+        a = np.maximum(g, np.float32(0))
+    elif act == "gelu_tanh":
+        a = np.float32(0.5) * g * (np.float32(1) + np.tanh(np.float32(0.7978845608028654) * (g + np.float32(0.044715) * g * g * g)))
+    else:
+        a = g / (np.float32(1.0) + np.exp(-g))
+    return a * u
+
+
+def gated_linear_recurrence(q: np.ndarray, k: np.ndarray, v: np.ndarray, z: np.ndarray, state: np.ndarray, root: float):
+    """o_t = S_t^T q_t with S_t = diag(sigmoid(z_t)^(1/root)) S_(t-1) + k_t v_t^T per head, float32: q, k, z
+    [seq, heads, dk], v [seq, heads, dv], state [heads, dk, dv] (updated in place).  Returns o [seq, heads, dv]
+    (not in xsmccc/llaisys)."""
+    q, k, v = q.astype(np.float32), k.astype(np.float32), v.astype(np.float32)
+    z = z.astype(np.float32)
+    a = np.exp(-(np.maximum(-z, 0) + np.log1p(np.exp(-np.abs(z)))) / np.float32(root)).astype(np.float32)
+    out = np.zeros(v.shape, dtype=np.float32)
+    for t in range(q.shape[0]):
+        state *= a[t][:, :, None]
+        state += k[t][:, :, None] * v[t][:, None, :]
+        out[t] = np.einsum("hkv,hk->hv", state, q[t])
+    return out

@@ -75,6 +75,7 @@ struct MmaAttnParams {
     int keep_first;         // with a window: keys before this position stay visible
     int pinned;             // cache pages ahead of the ring that are never overwritten
     int sink;               // the softmax's denominator has one more term e^0 (no value)
+    const float* sink_logits;   // [nh] or null: that term is e^(sink_logits[head]) instead (implies a sink)
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -517,8 +518,13 @@ __global__ void __launch_bounds__(THREADS) attn_mma_decode_kernel(MmaAttnParams 
     uint32_t qf[KSTEPS][4];
     load_q(qf, [&](int r) -> const bf16* { return qs + r * (DH + 8); }, lane);
     float o[DTILES][4], m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
-    if (p.sink && blockIdx.x == 0 && warp == 0) {          // the sink's term e^0, once per query head
+    if ((p.sink || p.sink_logits) && blockIdx.x == 0 && warp == 0) {          // the sink's term, once per query head
         m[0] = m[1] = 0.f;
+        if (p.sink_logits) {                               // rows are the group's heads; m is on the base-2 scale
+            const int r0 = lane >> 2;
+            m[0] = p.sink_logits[head0 + min(r0, n_heads - 1)] * 1.4426950408889634f;
+            m[1] = p.sink_logits[head0 + min(r0 + 8, n_heads - 1)] * 1.4426950408889634f;
+        }
         l[0] = l[1] = 1.f;
     }
 #pragma unroll
@@ -777,8 +783,8 @@ __global__ void __launch_bounds__(THREADS, 3) attn_mma_prefill_kernel(MmaAttnPar
     const int warp_hi = first_pos + warp * 16 + 15;                  // last position any row of this warp sees
     const int warp_lo = p.window > 0 ? max(0, first_pos + warp * 16 - p.window + 1) : 0;
     float o[DTILES][4], m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
-    if (p.sink) {                                                    // the sink's term e^0
-        m[0] = m[1] = 0.f;
+    if (p.sink || p.sink_logits) {                                   // the sink's term (m is on the base-2 scale)
+        m[0] = m[1] = p.sink_logits ? p.sink_logits[head] * 1.4426950408889634f : 0.f;
         l[0] = l[1] = 1.f;
     }
 #pragma unroll

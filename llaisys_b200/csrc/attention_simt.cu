@@ -146,29 +146,59 @@ __global__ void __launch_bounds__(WARPS * 32) attn_kernel(AttnParams p) {
     for (int it = it_lo; it < it_hi; ++it) {
         const int tile = it < n_kept ? it : tile_lo + it - n_kept;
         __syncthreads();                     // previous tile fully consumed (and Qs written)
-        for (int i = tid; i < LLB_PAGE * DH; i += WARPS * 32) {
-            int j = i / DH, d = i - j * DH;
-            int kp = tile * LLB_PAGE + j;
-            float kv = 0.f;
-            if ((kp >= key_lo || kp < keep) && kp <= last_pos) {
-                if (!DECODE && !p.all_from_cache && kp >= len_before)
-                    kv = to_f32(knew[(size_t)(tok0 + kp - len_before) * kv_stride + kvh * DH + d]);
-                else
-                    kv = to_f32(kpool[paged_row(table, p.ring, kp, kvh, p.nkvh, DH, p.pinned) + d]);
+        // A tile is one cache page (tiles start at multiples of LLB_PAGE): its page is looked up once; rows move in
+        // 16-byte pieces where the widths and the addresses allow it.
+        const int p0 = tile * LLB_PAGE;
+        const T* kpage = kpool + paged_row(table, p.ring, p0, kvh, p.nkvh, DH, p.pinned);
+        constexpr int VEC = 16 / (int)sizeof(T);
+        const bool kvec = DH % VEC == 0 && (((uintptr_t)kpool | (uintptr_t)knew) & 15) == 0 && kv_stride % VEC == 0;
+        if (kvec) {
+            for (int i = tid; i < LLB_PAGE * (DH / VEC); i += WARPS * 32) {
+                int j = i / (DH / VEC), d = (i - j * (DH / VEC)) * VEC;
+                int kp = p0 + j;
+                float vals[VEC];
+#pragma unroll
+                for (int e = 0; e < VEC; ++e) vals[e] = 0.f;
+                if ((kp >= key_lo || kp < keep) && kp <= last_pos) {
+                    const T* src = (!DECODE && !p.all_from_cache && kp >= len_before)
+                                       ? knew + (size_t)(tok0 + kp - len_before) * kv_stride + kvh * DH + d
+                                       : kpage + (size_t)j * DH + d;
+                    const uint4 raw = *reinterpret_cast<const uint4*>(src);
+                    const T* rv = reinterpret_cast<const T*>(&raw);
+#pragma unroll
+                    for (int e = 0; e < VEC; ++e) vals[e] = to_f32(rv[e]);
+                }
+#pragma unroll
+                for (int e = 0; e < VEC; ++e) Ks[j * (DH + 1) + d + e] = vals[e];
             }
-            Ks[j * (DH + 1) + d] = kv;
+        } else {
+            for (int i = tid; i < LLB_PAGE * DH; i += WARPS * 32) {
+                int j = i / DH, d = i - j * DH;
+                int kp = p0 + j;
+                float kv = 0.f;
+                if ((kp >= key_lo || kp < keep) && kp <= last_pos) {
+                    if (!DECODE && !p.all_from_cache && kp >= len_before)
+                        kv = to_f32(knew[(size_t)(tok0 + kp - len_before) * kv_stride + kvh * DH + d]);
+                    else
+                        kv = to_f32(kpage[(size_t)j * DH + d]);
+                }
+                Ks[j * (DH + 1) + d] = kv;
+            }
         }
-        for (int i = tid; i < (p.v_in_k ? 0 : LLB_PAGE * DV); i += WARPS * 32) {
-            int j = i / DV, d = i - j * DV;
-            int kp = tile * LLB_PAGE + j;
-            float vv = 0.f;
-            if ((kp >= key_lo || kp < keep) && kp <= last_pos) {
-                if (!DECODE && !p.all_from_cache && kp >= len_before)
-                    vv = to_f32(vnew[(size_t)(tok0 + kp - len_before) * kv_stride + kvh * DV + d]);
-                else
-                    vv = to_f32(vpool[paged_row(table, p.ring, kp, kvh, p.nkvh, DV, p.pinned) + d]);
+        if (!p.v_in_k) {
+            const T* vpage = vpool + paged_row(table, p.ring, p0, kvh, p.nkvh, DV, p.pinned);
+            for (int i = tid; i < LLB_PAGE * DV; i += WARPS * 32) {
+                int j = i / DV, d = i - j * DV;
+                int kp = p0 + j;
+                float vv = 0.f;
+                if ((kp >= key_lo || kp < keep) && kp <= last_pos) {
+                    if (!DECODE && !p.all_from_cache && kp >= len_before)
+                        vv = to_f32(vnew[(size_t)(tok0 + kp - len_before) * kv_stride + kvh * DV + d]);
+                    else
+                        vv = to_f32(vpage[(size_t)j * DV + d]);
+                }
+                Vs[j * DV + d] = vv;
             }
-            Vs[j * DV + d] = vv;
         }
         __syncthreads();
 #pragma unroll

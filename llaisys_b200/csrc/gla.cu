@@ -8,17 +8,16 @@
 // its sequence in order).  Everything that enters the recurrence besides the projections q, k, v is float32: the decay
 // logits z arrive in float32, a = exp(-softplus(-z) / tau) is formed here, the state and the sums stay float32.
 //
-//  * gla_scan: a block owns 32 value columns of one head of one sequence; a thread owns one column and every fourth
-//    key channel of it (KPT state values in registers); q, k, a and v of eight tokens at a time are staged in shared
-//    memory; o_t is completed by two shuffles.
+//  * gla_scan: a block owns a group of value columns of one head of one sequence; 4, 8 or 16 lanes share a column, each
+//    with a run of its key channels (KPT state values in registers); q, k, a and v of sixteen tokens at a time are
+//    staged in shared memory, the next sixteen being fetched into registers meanwhile; the chunk runs without a branch
+//    and every o_t is completed by shuffles among the lanes of its column, those of a chunk together.
 //  * gla_out: per (token, head) one warp: RMS norm of o over the value channels with a weight shared by the heads,
 //    times silu of the output gate.
 #include "common.cuh"
 
-constexpr int GLA_KS = 4;         // key-channel slices (lanes that share a value column)
-constexpr int GLA_COLS = 32;      // value columns of a block
-constexpr int GLA_THREADS = GLA_KS * GLA_COLS;
-constexpr int GLA_CHUNK = 8;      // tokens staged at a time
+constexpr int GLA_THREADS = 128;
+constexpr int GLA_CHUNK = 16;     // tokens staged at a time
 
 struct GlaParams {
     const void* q;            // packed projections [T, row_stride]: head h's queries at q + h * dk
@@ -35,18 +34,23 @@ struct GlaParams {
     float q_scale, inv_tau;
 };
 
-template <typename T, int KPT>
+// KS lanes share a value column, each with KPT consecutive key channels of it (KPT a multiple of 4); a block of 128
+// threads owns 128 / KS columns.  In shared memory a lane's channels of a token are KPT consecutive floats, the lanes'
+// groups KPT + 4 apart, so that the 16-byte reads of the lanes of a quarter-warp fall on different banks.
+template <typename T, int KS, int KPT>
 __global__ void __launch_bounds__(GLA_THREADS) gla_scan_kernel(GlaParams p) {
-    extern __shared__ float sm[];
-    constexpr int DKP = GLA_KS * KPT;                 // key channels, padded
-    float* sq = sm;                                   // [CHUNK][DKP]
-    float* sk = sq + GLA_CHUNK * DKP;
-    float* sa = sk + GLA_CHUNK * DKP;
-    float* sv = sa + GLA_CHUNK * DKP;                 // [CHUNK][COLS]
+    extern __shared__ __align__(16) float sm[];
+    constexpr int COLS = GLA_THREADS / KS;
+    constexpr int DKP = KS * KPT;                     // key channels, padded
+    constexpr int ROW = KS * (KPT + 4);               // floats of one token's q (or k, or a) in shared memory
+    float* sq = sm;                                   // [CHUNK][ROW]
+    float* sk = sq + GLA_CHUNK * ROW;
+    float* sa = sk + GLA_CHUNK * ROW;
+    float* sv = sa + GLA_CHUNK * ROW;                 // [CHUNK][COLS]
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const int part = lane & (GLA_KS - 1), jl = lane / GLA_KS;
-    const int cloc = warp * (32 / GLA_KS) + jl;       // column within the block
-    const int col = blockIdx.x * GLA_COLS + cloc;
+    const int part = lane & (KS - 1), jl = lane / KS;
+    const int cloc = warp * (32 / KS) + jl;           // column within the block
+    const int col = blockIdx.x * COLS + cloc;
     const int h = blockIdx.y, b = blockIdx.z;
     const int dk = p.dk, dv = p.dv;
     llb_grid_dependency_sync();
@@ -55,78 +59,148 @@ __global__ void __launch_bounds__(GLA_THREADS) gla_scan_kernel(GlaParams p) {
     float S[KPT];
 #pragma unroll
     for (int m = 0; m < KPT; ++m) {
-        int i = part + GLA_KS * m;
+        int i = part * KPT + m;
         S[m] = (i < dk && col < dv) ? st[(size_t)i * dv + col] : 0.f;
     }
     const T* qb = (const T*)p.q;
     const T* kb = (const T*)p.k;
     const T* vb = (const T*)p.v;
+    // A chunk's q, k, z and v are fetched into registers while the chunk before it is computed, and pass through the
+    // decay's arithmetic into shared memory when their turn comes: the walk never waits for a load it has just issued.
+    constexpr int NQ = (GLA_CHUNK * DKP + GLA_THREADS - 1) / GLA_THREADS;
+    constexpr int NV = (GLA_CHUNK * COLS + GLA_THREADS - 1) / GLA_THREADS;
+    float rq[NQ], rk[NQ], rz[NQ], rv[NV];
+    auto fetch = [&](int c0) {
+        const int nc = min(GLA_CHUNK, n - c0);
+#pragma unroll
+        for (int e = 0; e < NQ; ++e) {
+            const int idx = tid + e * GLA_THREADS, t = idx / DKP, i = idx - t * DKP;
+            rq[e] = rk[e] = 0.f;
+            rz[e] = INFINITY;                              // a decay of exactly one
+            if (idx < GLA_CHUNK * DKP && i < dk && t < nc) {
+                const size_t row = (size_t)(tok0 + c0 + t);
+                rq[e] = to_f32(qb[row * p.row_stride + h * dk + i]);
+                rk[e] = to_f32(kb[row * p.row_stride + h * dk + i]);
+                rz[e] = p.z[row * p.z_stride + h * dk + i];
+            }
+        }
+#pragma unroll
+        for (int e = 0; e < NV; ++e) {
+            const int idx = tid + e * GLA_THREADS, t = idx / COLS, c = idx - t * COLS;
+            const int cc = blockIdx.x * COLS + c;
+            rv[e] = (idx < GLA_CHUNK * COLS && cc < dv && t < nc) ? to_f32(vb[(size_t)(tok0 + c0 + t) * p.row_stride + h * dv + cc]) : 0.f;
+        }
+    };
+    fetch(0);
     for (int c0 = 0; c0 < n; c0 += GLA_CHUNK) {
         const int nc = min(GLA_CHUNK, n - c0);
         __syncthreads();
-        for (int idx = tid; idx < nc * DKP; idx += GLA_THREADS) {
-            int t = idx / DKP, i = idx - t * DKP;
-            float qv = 0.f, kv = 0.f, av = 1.f;
-            if (i < dk) {
-                size_t row = (size_t)(tok0 + c0 + t);
-                qv = to_f32(qb[row * p.row_stride + h * dk + i]) * p.q_scale;
-                kv = to_f32(kb[row * p.row_stride + h * dk + i]);
-                float zz = p.z[row * p.z_stride + h * dk + i];
+        // (token slots past the step's end hold a = 1, k = 0, q = 0: they leave the state as it is, so the tokens of a
+        // chunk run without a branch and their reductions overlap)
+#pragma unroll
+        for (int e = 0; e < NQ; ++e) {
+            const int idx = tid + e * GLA_THREADS;
+            if (idx < GLA_CHUNK * DKP) {
+                const int t = idx / DKP, i = idx - t * DKP;
+                const int at = t * ROW + (i / KPT) * (KPT + 4) + (i % KPT);
+                const float zz = rz[e];
+                sq[at] = rq[e] * p.q_scale;
+                sk[at] = rk[e];
                 // log sigmoid(z) = -softplus(-z) = -(max(-z, 0) + log(1 + e^-|z|))
-                av = expf(-(fmaxf(-zz, 0.f) + log1pf(expf(-fabsf(zz)))) * p.inv_tau);
+                sa[at] = expf(-(fmaxf(-zz, 0.f) + log1pf(expf(-fabsf(zz)))) * p.inv_tau);
             }
-            sq[idx] = qv;
-            sk[idx] = kv;
-            sa[idx] = av;
         }
-        for (int idx = tid; idx < nc * GLA_COLS; idx += GLA_THREADS) {
-            int t = idx / GLA_COLS, c = idx - t * GLA_COLS;
-            int cc = blockIdx.x * GLA_COLS + c;
-            sv[idx] = cc < dv ? to_f32(vb[(size_t)(tok0 + c0 + t) * p.row_stride + h * dv + cc]) : 0.f;
+#pragma unroll
+        for (int e = 0; e < NV; ++e) {
+            const int idx = tid + e * GLA_THREADS;
+            if (idx < GLA_CHUNK * COLS) sv[idx] = rv[e];
         }
         __syncthreads();
-        for (int t = 0; t < nc; ++t) {
-            const float vv = sv[t * GLA_COLS + cloc];
-            const float* a = sa + t * DKP + part;
-            const float* kk = sk + t * DKP + part;
-            const float* qq = sq + t * DKP + part;
-            float acc = 0.f;
+        if (c0 + GLA_CHUNK < n) fetch(c0 + GLA_CHUNK);
+        float acc[GLA_CHUNK];
 #pragma unroll
-            for (int m = 0; m < KPT; ++m) {
-                S[m] = fmaf(a[GLA_KS * m], S[m], kk[GLA_KS * m] * vv);
-                acc = fmaf(S[m], qq[GLA_KS * m], acc);
+        for (int t = 0; t < GLA_CHUNK; ++t) {
+            const float vv = sv[t * COLS + cloc];
+            const float4* a4 = reinterpret_cast<const float4*>(sa + t * ROW + part * (KPT + 4));
+            const float4* k4 = reinterpret_cast<const float4*>(sk + t * ROW + part * (KPT + 4));
+            const float4* q4 = reinterpret_cast<const float4*>(sq + t * ROW + part * (KPT + 4));
+            float a0 = 0.f, a1 = 0.f;                 // two chains, so that the sum does not wait on one
+#pragma unroll
+            for (int m = 0; m < KPT; m += 4) {
+                const float4 a = a4[m / 4], k = k4[m / 4], q = q4[m / 4];
+                S[m] = fmaf(a.x, S[m], k.x * vv);
+                a0 = fmaf(S[m], q.x, a0);
+                S[m + 1] = fmaf(a.y, S[m + 1], k.y * vv);
+                a1 = fmaf(S[m + 1], q.y, a1);
+                S[m + 2] = fmaf(a.z, S[m + 2], k.z * vv);
+                a0 = fmaf(S[m + 2], q.z, a0);
+                S[m + 3] = fmaf(a.w, S[m + 3], k.w * vv);
+                a1 = fmaf(S[m + 3], q.w, a1);
             }
-            acc += __shfl_xor_sync(0xffffffffu, acc, 1);
-            acc += __shfl_xor_sync(0xffffffffu, acc, 2);
-            if (part == 0 && col < dv) p.out[(size_t)(tok0 + c0 + t) * p.H * dv + h * dv + col] = acc;
+            acc[t] = a0 + a1;
+        }
+#pragma unroll
+        for (int o = 1; o < KS; o <<= 1) {
+#pragma unroll
+            for (int t = 0; t < GLA_CHUNK; ++t) acc[t] += __shfl_xor_sync(0xffffffffu, acc[t], o);
+        }
+        if (part == 0 && col < dv) {
+#pragma unroll
+            for (int t = 0; t < GLA_CHUNK; ++t)
+                if (t < nc) p.out[(size_t)(tok0 + c0 + t) * p.H * dv + h * dv + col] = acc[t];
         }
     }
 #pragma unroll
     for (int m = 0; m < KPT; ++m) {
-        int i = part + GLA_KS * m;
+        int i = part * KPT + m;
         if (i < dk && col < dv) st[(size_t)i * dv + col] = S[m];
     }
 }
 
-template <typename T, int KPT>
+template <typename T, int KS, int KPT>
 static int launch_scan(const GlaParams& p, int B, cudaStream_t stream) {
-    auto k = gla_scan_kernel<T, KPT>;
-    size_t smem = (size_t)(3 * GLA_CHUNK * GLA_KS * KPT + GLA_CHUNK * GLA_COLS) * sizeof(float);
-    dim3 grid((p.dv + GLA_COLS - 1) / GLA_COLS, p.H, B);
+    auto k = gla_scan_kernel<T, KS, KPT>;
+    constexpr int COLS = GLA_THREADS / KS;
+    size_t smem = (size_t)(3 * GLA_CHUNK * KS * (KPT + 4) + GLA_CHUNK * COLS) * sizeof(float);
+    dim3 grid((p.dv + COLS - 1) / COLS, p.H, B);
     if (grid.y > 65535 || grid.z > 65535) return (int)cudaErrorInvalidValue;
+    static bool configured = false;          // once per instantiation: not repeated inside a graph capture
+    if (!configured && smem > 48 * 1024) {
+        cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return (int)e;
+    }
+    configured = true;
     llb_launch(k, grid, dim3(GLA_THREADS), smem, stream, p);
     return llb_status();
 }
 
+template <typename T, int KS>
+static int launch_scan_ks(const GlaParams& p, int B, cudaStream_t stream) {
+    const int kpt = (p.dk + KS - 1) / KS;
+    if (kpt <= 4) return launch_scan<T, KS, 4>(p, B, stream);
+    if (kpt <= 8) return launch_scan<T, KS, 8>(p, B, stream);
+    if (kpt <= 16) return launch_scan<T, KS, 16>(p, B, stream);
+    if constexpr (KS <= 8) {
+        if (kpt <= 32) return launch_scan<T, KS, 32>(p, B, stream);
+    }
+    if constexpr (KS <= 4) {
+        if (kpt <= 64) return launch_scan<T, KS, 64>(p, B, stream);
+    }
+    return (int)cudaErrorInvalidValue;
+}
+
 // Runs the recurrence over the new tokens of every sequence of the step and writes o [T, H * dv] (float32).
-LLB_API int llb_gla_scan(GlaParams p, int dtype, int B, cudaStream_t stream) {
+// sms: multiprocessors of the device.  More lanes share a column (fewer columns a block, more blocks) while the blocks
+// would not fill the device and a lane still keeps four channels or more.
+LLB_API int llb_gla_scan(GlaParams p, int dtype, int B, int sms, cudaStream_t stream) {
     if (B == 0) return 0;
-    if (p.dk <= 0 || p.dv <= 0 || p.H <= 0 || p.dk > GLA_KS * 64) return (int)cudaErrorInvalidValue;
+    if (p.dk <= 0 || p.dv <= 0 || p.H <= 0 || p.dk > 256) return (int)cudaErrorInvalidValue;
+    int ks = 4;
+    while (ks < 16 && (long long)((p.dv + 128 / ks - 1) / (128 / ks)) * p.H * B < sms && p.dk >= 8 * ks) ks *= 2;
     LLB_DISPATCH_DTYPE(dtype, T, {
-        if (p.dk <= GLA_KS * 8) return launch_scan<T, 8>(p, B, stream);
-        if (p.dk <= GLA_KS * 16) return launch_scan<T, 16>(p, B, stream);
-        if (p.dk <= GLA_KS * 32) return launch_scan<T, 32>(p, B, stream);
-        return launch_scan<T, 64>(p, B, stream);
+        if (ks == 4) return launch_scan_ks<T, 4>(p, B, stream);
+        if (ks == 8) return launch_scan_ks<T, 8>(p, B, stream);
+        return launch_scan_ks<T, 16>(p, B, stream);
     });
     return 0;
 }

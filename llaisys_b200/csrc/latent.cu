@@ -162,7 +162,9 @@ LLB_API int llb_latent_append(const void* rows, int dtype, int T, int width, con
 
 // ------------------------------------------------------------------ per-head matrix product
 constexpr int HM_TOK = 16;        // tokens of a block
-constexpr int HM_COLS = 128;      // output columns of a block (one per thread)
+constexpr int HM_COLS = 32;       // output columns of a block (one per lane)
+constexpr int HM_WARPS = 4;       // warps of a block: each takes a quarter of the inputs
+constexpr int HM_THREADS = HM_WARPS * 32;
 
 struct HeadMatmulParams {
     const void* x;            // [T, x_stride]: head h's input at h * x_head
@@ -185,44 +187,63 @@ struct HeadMatmulParams {
 };
 
 template <typename T>
-__global__ void __launch_bounds__(HM_COLS) head_matmul_kernel(HeadMatmulParams p) {
-    extern __shared__ float xs[];                     // [HM_TOK][n_in]
-    const int tid = threadIdx.x, h = blockIdx.y;
+__global__ void __launch_bounds__(HM_THREADS) head_matmul_kernel(HeadMatmulParams p) {
+    extern __shared__ float xs[];                     // [HM_TOK][n_in], then the warps' partial sums [HM_WARPS][HM_TOK][HM_COLS]
+    float* part = xs + HM_TOK * p.n_in;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, h = blockIdx.y;
     const int t0 = blockIdx.x * HM_TOK, nt = min(HM_TOK, p.T - t0);
-    const int col = blockIdx.z * HM_COLS + tid;
+    const int col = blockIdx.z * HM_COLS + lane;
+    const T* mh = (const T*)p.m + (size_t)h * p.n_in * p.n_out + min(col, p.n_out - 1);
+    // the warp's share of the inputs; its first weights are fetched before the kernel ahead has finished
+    const int per = (p.n_in + HM_WARPS - 1) / HM_WARPS, d0 = warp * per, d1 = min(p.n_in, d0 + per);
     llb_grid_dependency_sync();
     const T* xb = (const T*)p.x;
-    for (int i = tid; i < nt * p.n_in; i += HM_COLS) {
+    for (int i = tid; i < HM_TOK * p.n_in; i += HM_THREADS) {
         int t = i / p.n_in, d = i - t * p.n_in;
-        xs[i] = to_f32(xb[(size_t)(t0 + t) * p.x_stride + h * p.x_head + d]);
+        xs[i] = t < nt ? to_f32(xb[(size_t)(t0 + t) * p.x_stride + h * p.x_head + d]) : 0.f;
     }
     __syncthreads();
     T* yb = (T*)p.y;
-    if (col < p.n_out) {
+    if (p.n_out > 0) {
         float acc[HM_TOK];
 #pragma unroll
         for (int t = 0; t < HM_TOK; ++t) acc[t] = 0.f;
-        const T* mh = (const T*)p.m + (size_t)h * p.n_in * p.n_out + col;
-        for (int d = 0; d < p.n_in; ++d) {
+        int d = d0;
+        for (; d + 8 <= d1; d += 8) {                 // eight weights in flight
+            float w[8];
+#pragma unroll
+            for (int e = 0; e < 8; ++e) w[e] = to_f32(mh[(size_t)(d + e) * p.n_out]);
+#pragma unroll
+            for (int t = 0; t < HM_TOK; ++t) {
+                const float* x = xs + t * p.n_in + d;
+                float a = acc[t];
+#pragma unroll
+                for (int e = 0; e < 8; ++e) a = fmaf(x[e], w[e], a);
+                acc[t] = a;
+            }
+        }
+        for (; d < d1; ++d) {
             const float w = to_f32(mh[(size_t)d * p.n_out]);
 #pragma unroll
-            for (int t = 0; t < HM_TOK; ++t) acc[t] = fmaf(xs[t * p.n_in + d], w, acc[t]);   // rows past nt hold stale data, never stored
+            for (int t = 0; t < HM_TOK; ++t) acc[t] = fmaf(xs[t * p.n_in + d], w, acc[t]);
         }
 #pragma unroll
-        for (int t = 0; t < HM_TOK; ++t) {
-            if (t < nt) {
-                float v = acc[t];
-                if (p.gate) {
-                    float g = to_f32(((const T*)p.gate)[(size_t)(t0 + t) * p.gate_stride + h]);
-                    v *= 1.0f / (1.0f + expf(-g));
-                }
-                yb[(size_t)(t0 + t) * p.y_stride + h * p.y_head + col] = from_f32<T>(v);
+        for (int t = 0; t < HM_TOK; ++t) part[(warp * HM_TOK + t) * HM_COLS + lane] = acc[t];
+        __syncthreads();
+        // warp w finishes the tokens w, w + 4, ...: the four partial sums in a fixed order
+        for (int t = warp; t < nt; t += HM_WARPS) {
+            float v = (part[t * HM_COLS + lane] + part[(HM_TOK + t) * HM_COLS + lane]) +
+                      (part[(2 * HM_TOK + t) * HM_COLS + lane] + part[(3 * HM_TOK + t) * HM_COLS + lane]);
+            if (p.gate) {
+                float g = to_f32(((const T*)p.gate)[(size_t)(t0 + t) * p.gate_stride + h]);
+                v *= 1.0f / (1.0f + expf(-g));
             }
+            if (col < p.n_out) yb[(size_t)(t0 + t) * p.y_stride + h * p.y_head + col] = from_f32<T>(v);
         }
     }
     if (blockIdx.z == 0 && p.tail > 0) {
         const int half = p.rot >> 1;
-        for (int i = tid; i < nt * half; i += HM_COLS) {
+        for (int i = tid; i < nt * half; i += HM_THREADS) {
             int t = i / half, j = i - t * half;
             int pos = p.tok_pos[t0 + t];
             if (pos < 0 || pos >= p.table_rows) {
@@ -237,7 +258,7 @@ __global__ void __launch_bounds__(HM_COLS) head_matmul_kernel(HeadMatmulParams p
             dst[2 * j + 1] = from_f32<T>(b * c + a * s);
         }
         const int rest = p.tail - p.rot;
-        for (int i = tid; i < nt * rest; i += HM_COLS) {
+        for (int i = tid; i < nt * rest; i += HM_THREADS) {
             int t = i / rest, j = p.rot + i - t * rest;
             yb[(size_t)(t0 + t) * p.y_stride + h * p.y_head + p.n_out + j] =
                 xb[(size_t)(t0 + t) * p.x_stride + h * p.x_head + p.n_in + j];
@@ -247,14 +268,69 @@ __global__ void __launch_bounds__(HM_COLS) head_matmul_kernel(HeadMatmulParams p
 
 LLB_API int llb_head_matmul(HeadMatmulParams p, int dtype, cudaStream_t stream) {
     if (p.T == 0 || p.H == 0) return 0;
-    size_t smem = (size_t)HM_TOK * (p.n_in > 0 ? p.n_in : 1) * sizeof(float);
+    size_t smem = (size_t)(HM_TOK * p.n_in + HM_WARPS * HM_TOK * HM_COLS) * sizeof(float);
     if (smem > 200 * 1024) return (int)cudaErrorInvalidValue;
     dim3 grid((p.T + HM_TOK - 1) / HM_TOK, p.H, p.n_out > 0 ? (p.n_out + HM_COLS - 1) / HM_COLS : 1);
     if (grid.y > 65535 || grid.z > 65535) return (int)cudaErrorInvalidValue;
     LLB_DISPATCH_DTYPE(dtype, TT, {
         auto k = head_matmul_kernel<TT>;
         if (smem > 48 * 1024) cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        llb_launch(k, grid, dim3(HM_COLS), smem, stream, p);
+        llb_launch(k, grid, dim3(HM_THREADS), smem, stream, p);
+    });
+    return llb_status();
+}
+
+// ------------------------------------------------------------------ rotation and gate alone, in place
+// x [T, stride]: H heads of `head` elements; the pairs (2i, 2i+1), i < rot / 2, of the elements from `off` on are rotated.
+template <typename T>
+__global__ void __launch_bounds__(128) rope_pairs_kernel(T* __restrict__ x, int stride, int H, int head, int off, int rot,
+                                                         const float* __restrict__ cos_t, const float* __restrict__ sin_t,
+                                                         int table_rows, const int* __restrict__ tok_pos, int* err) {
+    const int t = blockIdx.x, pos = tok_pos[t], half = rot >> 1;
+    if (pos < 0 || pos >= table_rows) {
+        if (threadIdx.x == 0) atomicExch(err, 2);
+        return;
+    }
+    llb_grid_dependency_sync();
+    T* row = x + (size_t)t * stride;
+    for (int i = threadIdx.x; i < H * half; i += blockDim.x) {
+        const int h = i / half, j = i - h * half;
+        const float c = cos_t[(size_t)pos * half + j], s = sin_t[(size_t)pos * half + j];
+        T* e = row + h * head + off + 2 * j;
+        const float a = to_f32(e[0]), b = to_f32(e[1]);
+        e[0] = from_f32<T>(a * c - b * s);
+        e[1] = from_f32<T>(b * c + a * s);
+    }
+}
+
+LLB_API int llb_rope_pairs(void* x, int dtype, int T, int stride, int H, int head, int off, int rot, const float* cos_t,
+                           const float* sin_t, int table_rows, const int* tok_pos, int* err, cudaStream_t stream) {
+    if (T == 0 || rot <= 0) return 0;
+    LLB_DISPATCH_DTYPE(dtype, TT, {
+        llb_launch(rope_pairs_kernel<TT>, dim3(T), dim3(128), 0, stream, (TT*)x, stride, H, head, off, rot, cos_t, sin_t,
+                   table_rows, tok_pos, err);
+    });
+    return llb_status();
+}
+
+// x[t, h, :] *= sigmoid(gate[t * gate_stride + h]) for x [T, H * width] (contiguous)
+template <typename T>
+__global__ void head_gate_kernel(T* __restrict__ x, const T* __restrict__ gate, int gate_stride, int H, int width, size_t n) {
+    llb_grid_dependency_sync();
+    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    size_t th = i / width, t = th / H;
+    int h = (int)(th - t * H);
+    float g = to_f32(gate[t * gate_stride + h]);
+    x[i] = from_f32<T>(to_f32(x[i]) / (1.0f + expf(-g)));
+}
+
+LLB_API int llb_head_gate(void* x, const void* gate, int gate_stride, int dtype, int T, int H, int width, cudaStream_t stream) {
+    size_t n = (size_t)T * H * width;
+    if (n == 0) return 0;
+    LLB_DISPATCH_DTYPE(dtype, TT, {
+        llb_launch(head_gate_kernel<TT>, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, stream, (TT*)x, (const TT*)gate,
+                   gate_stride, H, width, n);
     });
     return llb_status();
 }

@@ -9,7 +9,7 @@ from typing import Optional
 import torch
 
 from ..csrc.build import load_module
-from .ops import DT, KernelError, _AttnParams, _attn_lib, _check, _dt, _fn, _need_cuda, _ptr, _stream
+from .ops import DT, KernelError, _AttnParams, _attn_lib, _check, _dt, _fn, _need_cuda, _ptr, _sm_count, _stream
 
 
 class _GlaParams(ctypes.Structure):
@@ -39,8 +39,8 @@ def gla_scan(proj: torch.Tensor, H: int, dk: int, dv: int, z: torch.Tensor, stat
     p.row_stride, p.z, p.z_stride = proj.stride(0), z.data_ptr(), z.stride(0)
     p.state, p.seq_start, p.seq_slot, p.out = state.data_ptr(), seq_start.data_ptr(), seq_slot.data_ptr(), out.data_ptr()
     p.H, p.dk, p.dv, p.q_scale, p.inv_tau = H, dk, dv, q_scale, 1.0 / decay_root
-    f = _fn(load_module("gla.cu"), "llb_gla_scan", [_GlaParams, c_int, c_int, c_void_p])
-    _check(f(p, _dt(proj), n_seqs, _stream()), "gated linear attention (recurrence)")
+    f = _fn(load_module("gla.cu"), "llb_gla_scan", [_GlaParams, c_int, c_int, c_int, c_void_p])
+    _check(f(p, _dt(proj), n_seqs, _sm_count(proj.device), _stream()), "gated linear attention (recurrence)")
     return out
 
 
@@ -145,6 +145,29 @@ def head_matmul(x: torch.Tensor, m: torch.Tensor, *, tail: int = 0, tables=None,
     f = _fn(load_module("latent.cu"), "llb_head_matmul", [_HeadMatmulParams, c_int, c_void_p])
     _check(f(p, _dt(x), _stream()), "per-head matrix product")
     return y
+
+
+def rope_pairs_(x: torch.Tensor, H: int, head: int, off: int, tables, tok_pos: torch.Tensor, err: torch.Tensor) -> None:
+    """In place on x [T, >= H head] (row stride free): of every head's elements from `off` on, the pairs (2i, 2i+1),
+    i < rot / 2, are rotated by tables = (cos, sin, rot) at the tokens' positions."""
+    _need_cuda(x, tok_pos)
+    if tables is None:
+        return
+    cos, sin, rot = tables
+    assert x.stride(1) == 1 and off + rot <= head
+    f = _fn(load_module("latent.cu"), "llb_rope_pairs", [c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p,
+                                                         c_int, c_void_p, c_void_p, c_void_p])
+    _check(f(_ptr(x), _dt(x), x.shape[0], x.stride(0), H, head, off, rot, _ptr(cos), _ptr(sin), cos.shape[0], _ptr(tok_pos), _ptr(err),
+             _stream()), "rotation of neighbouring pairs")
+
+
+def head_gate_(x: torch.Tensor, gate: torch.Tensor, H: int) -> torch.Tensor:
+    """In place on x [T, H width] (contiguous): head h of token t times sigmoid(gate[t, h]) (gate a [T, >= H] view)."""
+    _need_cuda(x, gate)
+    assert x.is_contiguous() and gate.dtype == x.dtype and gate.stride(1) == 1 and x.shape[1] % H == 0
+    f = _fn(load_module("latent.cu"), "llb_head_gate", [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p])
+    _check(f(_ptr(x), _ptr(gate), gate.stride(0), _dt(x), x.shape[0], H, x.shape[1] // H, _stream()), "per-head output gate")
+    return x
 
 
 LATENT_MAX_ROW = 640          # the widest cache row (latent + rotated part) the attention kernel's key tile holds

@@ -495,8 +495,9 @@ def _gemm_tc(x, weight, bias, out, dual_offset=0, plan=None):
 
 
 def linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] = None,
-           out_dtype: Optional[torch.dtype] = None, plan=None) -> torch.Tensor:
-    """x [M, K] (row stride free) times weight [N, K] transposed, plus bias [N]; float32 accumulation.
+           out_dtype: Optional[torch.dtype] = None, plan=None, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """x [M, K] (row stride free) times weight [N, K] transposed, plus bias [N]; float32 accumulation.  `out`: an
+    [M, N] tensor or view (row stride free) that receives the result instead of a new tensor.
 
     bfloat16 operands with K a multiple of 8 run on the tensor cores (csrc/gemm_tc.cu); everything
     else (float32, a 32-bit weight under 16-bit activations, odd K) on the CUDA cores (csrc/gemm_simt.cu)."""
@@ -506,10 +507,13 @@ def linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] =
     if K != K2:
         raise KernelError(f"linear: x has {K} columns but the weight has {K2}")
     assert x.stride(1) == 1 and weight.is_contiguous()
-    out = torch.empty((M, N), dtype=out_dtype or x.dtype, device=x.device)
+    if out is None:
+        out = torch.empty((M, N), dtype=out_dtype or x.dtype, device=x.device)
+    else:
+        assert out.shape == (M, N) and out.stride(1) == 1 and out.is_cuda
     if M == 0:
         return out
-    if _tc_ok(x, weight, bias):
+    if _tc_ok(x, weight, bias) and (out.is_contiguous() or (out.data_ptr() % 16 == 0 and out.stride(0) % 8 == 0 and N % 8 == 0)):
         _gemm_tc(x, weight, bias, out, plan=plan)
         return out
     lib = load_module("gemm_simt.cu")
@@ -628,7 +632,7 @@ class _MmaAttnParams(ctypes.Structure):
                 ("scale", c_float), ("all_from_cache", c_int), ("n_splits", c_int), ("part_o", c_void_p),
                 ("part_ml", c_void_p), ("rope_cos", c_void_p), ("rope_sin", c_void_p), ("rope_rows", c_int),
                 ("append_new", c_int), ("cluster", c_int), ("err", c_void_p),
-                ("keep_first", c_int), ("pinned", c_int), ("sink", c_int)]
+                ("keep_first", c_int), ("pinned", c_int), ("sink", c_int), ("sink_logits", c_void_p)]
 
 
 MMA_ATTENTION = True                         # tests switch the tensor-core attention off to compare
@@ -700,14 +704,17 @@ def _attn_lib(dh: int, dv: Optional[int] = None):
 class AttnExtras:
     """What the plain causal (windowed) softmax attention does not have: values of a width of their own, first keys
     that stay visible behind a window (`keep_first`, held in `pinned` pages ahead of the cache ring), and a
-    value-less sink term of score 0 in the softmax's denominator."""
+    value-less sink term in the softmax's denominator: of score 0 (`sink`), or of a learned score per query head
+    (`sink_logits`, float32 [heads])."""
     value_dim: Optional[int] = None
     keep_first: int = 0
     pinned: int = 0
     sink: bool = False
+    sink_logits: Optional[torch.Tensor] = None
 
     def plain(self, dh: int) -> bool:
-        return self.value_dim in (None, dh) and not self.keep_first and not self.pinned and not self.sink
+        return (self.value_dim in (None, dh) and not self.keep_first and not self.pinned and not self.sink
+                and self.sink_logits is None)
 
 
 def _attn_params(qkv, out, nh, nkvh, dh, kpool, vpool, page_table, ring, seq_start, seq_len_before,
@@ -719,6 +726,9 @@ def _attn_params(qkv, out, nh, nkvh, dh, kpool, vpool, page_table, ring, seq_sta
     p.v_new = qkv.data_ptr() + (nh + nkvh) * dh * es
     if extras is not None:
         p.keep_first, p.pinned, p.sink = (extras.keep_first if window else 0), extras.pinned, int(extras.sink)
+        if extras.sink_logits is not None:
+            assert extras.sink_logits.dtype == torch.float32 and extras.sink_logits.numel() == nh
+            p.sink_logits = extras.sink_logits.data_ptr()
     p.row_stride = qkv.stride(0)
     p.out = out.data_ptr()
     p.kpool, p.vpool = kpool.data_ptr(), vpool.data_ptr()
@@ -834,6 +844,7 @@ def _attention_extras(decode, qkv, nh, nkvh, dh, kpool, vpool, page_table, ring,
     dv = extras.value_dim or dh
     out = torch.empty((qkv.shape[0], nh * dv), dtype=qkv.dtype, device=qkv.device)
     if (not decode and dv == dh and all_from_cache and prefill_tc_ok(qkv.dtype, dh) and not extras.pinned and scale > 0
+            and extras.sink_logits is None
             and ring >= page_table.shape[1] and qkv.stride(0) % 8 == 0):
         # a cache that keeps every key, head size 64 or 128: the tcgen05 prefill kernel, as for the plain attention
         _attention_prefill_tc(qkv, out, nh, nkvh, dh, kpool, vpool, page_table, seq_start, seq_len_before, n_seqs, max_new,

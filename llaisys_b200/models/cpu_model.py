@@ -19,9 +19,10 @@ from .. import cpu_ops
 from ..config.spec import ModelSpec, PartSpec
 
 _KNOWN = {"embedding": {"token_embedding", "scaled_pair_embedding"}, "norm": {"rms_norm"},
-          "mixer": {"gqa_attention", "windowed_sink_attention"}, "ffn": {"swiglu_mlp", "routed_experts"},
-          "block": {"pre_norm_residual", "parallel_residual"}, "head": {"lm_head"},
-          "position": {"rope_half_split", "rope_leading"}}
+          "mixer": {"gqa_attention", "windowed_sink_attention", "gated_linear_attention", "latent_attention"},
+          "ffn": {"swiglu_mlp", "routed_experts", "gated_mlp"},
+          "block": {"pre_norm_residual", "parallel_residual", "sandwich_residual"}, "head": {"lm_head"},
+          "position": {"rope_half_split", "rope_leading", "rope_interleaved"}}
 
 
 class CpuModel:
@@ -60,7 +61,81 @@ class CpuModel:
 
     # ---- parts
     def _norm(self, p: PartSpec, x):
-        return cpu_ops.rms_norm(x, self.w[p.tensor_name(p.params.get("tensor", "weight"))], p.params["eps"])
+        w = self.w[p.tensor_name(p.params.get("tensor", "weight"))]
+        if p.params.get("offset"):
+            w = w.astype(np.float32) + np.float32(p.params["offset"])       # stored as the distance from the offset
+        return cpu_ops.rms_norm(x, w, p.params["eps"])
+
+    def _gla(self, p: PartSpec, x, store: dict, key):
+        a = p.params
+        H, dk, dv = a["num_heads"], a["key_dim"], a["value_dim"]
+        n = dict({"q": "q", "k": "k", "v": "v", "g": "g", "o": "o", "norm": "norm", "a1": "a1", "a2": "a2", "a2_bias": "a2.b"},
+                 **(a.get("names") or {}))
+        w = lambda k: self.w[p.tensor_name(n[k])]
+        T = x.shape[0]
+        q = cpu_ops.linear(x, w("q")).reshape(T, H, dk) * np.float32(a.get("query_scale", 1.0))
+        k = cpu_ops.linear(x, w("k")).reshape(T, H, dk)
+        v = cpu_ops.linear(x, w("v")).reshape(T, H, dv)
+        z = cpu_ops.linear(cpu_ops.linear(x, w("a1")), w("a2"), w("a2_bias")).reshape(T, H, dk)
+        if key not in store:
+            store[key] = np.zeros((H, dk, dv), dtype=np.float32)
+        o = cpu_ops.gated_linear_recurrence(q, k, v, z, store[key], a["decay_root"])
+        o = cpu_ops.rms_norm(o, w("norm"), a["eps"]).reshape(T, H * dv)
+        g = cpu_ops.linear(x, w("g"))
+        return cpu_ops.linear(o * (g / (np.float32(1) + np.exp(-g))), w("o"))
+
+    def _latent(self, p: PartSpec, x, positions, store: dict, key, owner):
+        """The heads' keys and values are made from the cached latents here (the engine carries the queries into the
+        latent space instead)."""
+        a = p.params
+        H, dn, dr, dv, r = a["num_heads"], a["nope_dim"], a["rope_dim"], a["value_dim"], a["kv_rank"]
+        n = dict({"dq": "dq", "dq_norm": "dq.norm", "uq": "uq", "dkv": "dkv", "dkv_norm": "dkv.norm", "uk": "uk", "uv": "uv",
+                  "sink": "sink", "g": "g", "o": "o"}, **(a.get("names") or {}))
+        w = lambda k: self.w[p.tensor_name(n[k])]
+        pos = a["position"].params
+        rot = lambda t: cpu_ops.rope_pairs(t, positions, pos["dims"], pos["base"], pos.get("yarn"))
+        T = x.shape[0]
+        cq = cpu_ops.rms_norm(cpu_ops.linear(x, w("dq")), w("dq_norm"), a["eps"])
+        q = cpu_ops.linear(cq, w("uq")).reshape(T, H, dn + dr)
+        q = np.concatenate([q[:, :, :dn], rot(q[:, :, dn:])], axis=-1)
+        if owner is None:
+            d = cpu_ops.linear(x, w("dkv"))
+            c, kr = cpu_ops.rms_norm(d[:, :r], w("dkv_norm"), a["eps"]), rot(d[:, None, r:])[:, 0]
+            old = store.get(key)
+            store[key] = (c, kr) if old is None else (np.concatenate([old[0], c]), np.concatenate([old[1], kr]))
+            cs, krs = store[key]
+        else:
+            cs, krs = owner[key]
+        L = cs.shape[0]
+        k = np.concatenate([cpu_ops.linear(cs, w("uk")).reshape(L, H, dn), np.broadcast_to(krs[:, None, :], (L, H, dr))], axis=-1)
+        v = cpu_ops.linear(cs, w("uv")).reshape(L, H, dv)
+        o = cpu_ops.self_attention(q, k, v, a["scale"], a.get("window"), sink_logits=w("sink") if a.get("sink") else None)
+        if a.get("head_gate"):
+            g = cpu_ops.linear(x, w("g"))
+            o = o * (np.float32(1) / (np.float32(1) + np.exp(-g)))[:, :, None]
+        return cpu_ops.linear(o.reshape(T, H * dv), w("o"))
+
+    def _gated_mlp(self, p: PartSpec, x):
+        n = dict({"gate": "gate_proj.weight", "up": "up_proj.weight", "down": "down_proj.weight"}, **(p.params.get("names") or {}))
+        g, u = cpu_ops.linear(x, self.w[p.tensor_name(n["gate"])]), cpu_ops.linear(x, self.w[p.tensor_name(n["up"])])
+        return cpu_ops.linear(cpu_ops.glu(g, u, p.params.get("act", "silu")), self.w[p.tensor_name(n["down"])])
+
+    def _part(self, sub, h, positions, store, m, owner):
+        """One part's output for normed input h."""
+        kind = sub.part.kind
+        if kind == "gated_linear_attention":
+            return self._gla(sub.part, h, store, m)
+        if kind == "latent_attention":
+            return self._latent(sub.part, h, positions, store, m, owner)
+        if kind == "windowed_sink_attention":
+            return self._sink_attention(sub.part, h, positions, store, m, owner)
+        if kind == "gqa_attention":
+            return self._attention(sub.part, h, positions, store, m, owner)
+        if kind == "routed_experts":
+            return self._routed(sub.part, h)
+        if kind == "gated_mlp":
+            return self._gated_mlp(sub.part, h)
+        return self._mlp(sub.part, h)
 
     def _embed(self, tokens):
         p = self.spec.embedding
@@ -155,12 +230,12 @@ class CpuModel:
             for sub in layer.sublayers:
                 src = x_in if parallel else x
                 h = self._norm(sub.norm, src) if sub.norm is not None else src
+                y = self._part(sub, h, positions, self.cache[c], m, owner)
                 if sub.category == "mixer":
-                    attend = self._sink_attention if sub.part.kind == "windowed_sink_attention" else self._attention
-                    x = cpu_ops.add(attend(sub.part, h, positions, self.cache[c], m, owner), x)
                     m += 1
-                else:
-                    x = cpu_ops.add((self._routed if sub.part.kind == "routed_experts" else self._mlp)(sub.part, h), x)
+                if layer.block == "sandwich_residual":       # the part's output is normed and scaled on its way into the stream
+                    y = self._norm(sub.post_norm, y) * np.float32(layer.params.get("mult", 1.0))
+                x = cpu_ops.add(y, x)
         self.length += len(tokens)
         x = self._norm(self.spec.final_norm, x)
         head = self.spec.head

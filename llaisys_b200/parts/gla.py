@@ -16,8 +16,10 @@ class GatedLinearAttention(Mixer):
         S <- diag(a) S + k v^T,      o = S^T q
         out = Wo (rms_norm(o over value_dim; weight shared by heads) * silu(Wg h))
 
-    q, k, v, the output gate and the bottleneck are one matrix product; the decay logits leave their product in float32,
-    and everything from there to o (the decay, the state, the sums) is float32.  One kernel runs the recurrence for
+    q, k and v are one matrix product whose output stays float32 in both precisions (o is a sum with cancellation that
+    a norm then scales to unit size, so rounding q, k, v to 16 bits would be magnified wherever o happens to be small);
+    the output gate and the bottleneck are a second one; the decay logits leave their product in float32, and everything
+    from there to o (the decay, the state, the sums) is float32.  One kernel runs the recurrence for
     whole prompts, portions and single tokens.  The bottleneck's size is the shape of `a1`.
 
     params: hidden_size, num_heads, key_dim, value_dim, decay_root, query_scale, eps, decay_rank (random weights only),
@@ -38,7 +40,7 @@ class GatedLinearAttention(Mixer):
         self.rank = int(p.get("decay_rank", 16))
         self.names = dict({"q": "q", "k": "k", "v": "v", "g": "g", "o": "o", "norm": "norm", "a1": "a1", "a2": "a2",
                            "a2_bias": "a2.b"}, **(p.get("names") or {}))
-        self.w_in = self.w_a2 = self.b_a2 = self.w_norm = self.w_o = None
+        self.w_in = self.w_gate = self.w_a2 = self.b_a2 = self.w_norm = self.w_o = None
 
     def state_size(self):
         return self.nh * self.dk * self.dv
@@ -55,21 +57,27 @@ class GatedLinearAttention(Mixer):
         self.rank = int(tensors[n["a1"]].shape[0])
         if tensors[n["a2"]].shape[1] != self.rank:
             raise ValueError(f"the decay's two matrices do not fit: {tuple(tensors[n['a1']].shape)} and {tuple(tensors[n['a2']].shape)}")
-        ts = [tensors[n[k]] for k in ("q", "k", "v", "g", "a1")]
-        dt = ts[0].dtype
-        for t in ts[1:]:
-            dt = torch.promote_types(dt, t.dtype)
-        self.w_in = torch.cat([t.to(dt) for t in ts], dim=0).contiguous()
+        def fuse(keys):
+            ts = [tensors[n[k]] for k in keys]
+            dt = ts[0].dtype
+            for t in ts[1:]:
+                dt = torch.promote_types(dt, t.dtype)
+            return torch.cat([t.to(dt) for t in ts], dim=0).contiguous()
+
+        self.w_in = fuse(("q", "k", "v"))
+        self.w_gate = fuse(("g", "a1"))
         self.w_a2 = tensors[n["a2"]].contiguous()
         self.b_a2 = tensors[n["a2_bias"]].float().contiguous()
         self.w_norm = tensors[n["norm"]].contiguous()
         self.w_o = tensors[n["o"]].contiguous()
 
     def forward(self, x, ctx, call):
-        K, V = self.nh * self.dk, self.nh * self.dv
-        proj = kernels.linear(x, self.w_in)                                          # [T, q | k | v | g | bottleneck]
-        z = kernels.linear(proj[:, 2 * K + 2 * V:], self.w_a2, self.b_a2, out_dtype=torch.float32)
-        o = kernels.gla_scan(proj, self.nh, self.dk, self.dv, z, ctx.state(call), ctx.seq_start, ctx.seq_slot, ctx.n_seqs,
+        from .mlp import delta_dtype
+        V = self.nh * self.dv
+        qkv = kernels.linear(x, self.w_in, out_dtype=torch.float32)                  # [T, q | k | v]
+        gate = kernels.linear(x, self.w_gate)                                        # [T, g | bottleneck]
+        z = kernels.linear(gate[:, V:], self.w_a2, self.b_a2, out_dtype=torch.float32)
+        o = kernels.gla_scan(qkv, self.nh, self.dk, self.dv, z, ctx.state(call), ctx.seq_start, ctx.seq_slot, ctx.n_seqs,
                              self.q_scale, self.root)
-        y = kernels.gla_out(o, proj[:, 2 * K + V:2 * K + 2 * V], self.w_norm, self.nh, self.dv, self.eps, x.dtype)
-        return kernels.linear(y, self.w_o, out_dtype=torch.float32)
+        y = kernels.gla_out(o, gate[:, :V], self.w_norm, self.nh, self.dv, self.eps, x.dtype)
+        return kernels.linear(y, self.w_o, out_dtype=delta_dtype(y))

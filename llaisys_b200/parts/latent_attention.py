@@ -3,7 +3,6 @@ from __future__ import annotations
 import torch
 
 from .. import kernels
-from .attention import decode_splits
 from .base import KVNeed, Mixer, TensorDecl, build_part, register_part
 
 
@@ -24,6 +23,12 @@ class LatentAttention(Mixer):
     product), attention runs over the cached rows as one key/value head shared by all query heads (key: the whole row,
     value: its first kv_rank elements), and the latent result is carried into each head's value space.  Scores,
     softmax and all norms are float32.
+
+    A step of whole prompts (no sequence of the step has history) in bfloat16, with heads whose query/key and value sizes
+    are equal and fit the tensor-core attention kernel, goes the other way round: the heads' keys and values of the
+    step's tokens are made from the step's rows by one matrix product (Wuk, an identity block that copies the rotated
+    part into every head, and Wuv stacked), and the framework's tensor-core attention runs over them as ordinary heads,
+    with the learned sink as its extra term; nothing is read from the cache, which is still appended to as always.
 
     `own_kv` false: the layer has no Wdkv and reads the rows another layer cached (the run order's `cache_of`), with
     its own up projections, queries, window and everything else.
@@ -61,6 +66,7 @@ class LatentAttention(Mixer):
         self.names = dict({"dq": "dq", "dq_norm": "dq.norm", "uq": "uq", "dkv": "dkv", "dkv_norm": "dkv.norm", "uk": "uk",
                            "uv": "uv", "sink": "sink", "g": "g", "o": "o"}, **(p.get("names") or {}))
         self.w_in = self.w_uq = self.w_uk = self.w_uv_t = self.w_o = self.w_qn = self.w_kvn = self.sink_logits = None
+        self.w_kv_heads = None
 
     def prepare(self, max_positions):
         if self.position is not None:
@@ -89,6 +95,9 @@ class LatentAttention(Mixer):
         dt = ts[0].dtype
         for t in ts[1:]:
             dt = torch.promote_types(dt, t.dtype)
+        rows = sum(t.shape[0] for t in ts)
+        if rows % 8:                                   # whole 16-byte pieces of output rows: the faster products want them
+            ts.append(torch.zeros((8 - rows % 8, self.hidden), dtype=dt, device=ts[0].device))
         self.w_in = torch.cat([t.to(dt) for t in ts], dim=0).contiguous()       # [query latent | kv latent, key part | gates]
         self.gate_off = self.q_rank + (self.row if self.own_kv else 0)
         self.w_uq = tensors[n["uq"]].contiguous()
@@ -98,13 +107,25 @@ class LatentAttention(Mixer):
         self.w_qn = tensors[n["dq_norm"]].float().contiguous()
         self.w_kvn = tensors[n["dkv_norm"]].float().contiguous() if self.own_kv else None
         self.sink_logits = tensors[n["sink"]].float().contiguous() if self.sink else None
+        dk = self.dn + self.dr
+        if self.w_uq.dtype == torch.bfloat16 and dk == self.dv and dk % 16 == 0 and dk <= 128 and self.row % 8 == 0:
+            # rows [c | k_r] -> every head's [Wuk[h] c | k_r], then every head's Wuv[h] c
+            w = torch.zeros((H * dk + H * self.dv, self.row), dtype=self.w_uq.dtype, device=self.w_uq.device)
+            keys = w[:H * dk].view(H, dk, self.row)
+            keys[:, :self.dn, :self.kv_rank] = tensors[n["uk"]].reshape(H, self.dn, self.kv_rank)
+            keys[:, self.dn:, self.kv_rank:] = torch.eye(self.dr, dtype=w.dtype, device=w.device)
+            w[H * dk:, :self.kv_rank] = tensors[n["uv"]]
+            self.w_kv_heads = w
 
     def _splits(self, ctx) -> int:
+        """Slices of the key range in decode: all query heads of a sequence share one block per slice, so enough slices to
+        fill the device, at most one per page that the window (or the widest page table of the step) can span: a function
+        of the step's shape alone, so a captured step stays valid as sequences grow."""
         from ..cache.kv import ring_pages
-        splits = decode_splits(ctx, 1)
+        pages = max(ctx.widths) if ctx.widths else 1
         if self.window is not None:
-            splits = min(splits, ring_pages(self.window))
-        return max(1, min(splits, 64))
+            pages = min(pages, ring_pages(self.window))
+        return max(1, min((2 * ctx.sm_count) // max(1, ctx.n_seqs), pages, 64))
 
     def forward(self, x, ctx, call):
         kv = ctx.kv(call)
@@ -120,6 +141,19 @@ class LatentAttention(Mixer):
         after = ring_cache and not ctx.is_decode          # a ring is appended to after a step of several tokens
         cq, rows = kernels.latent_prep(proj, self.q_rank, self.kv_rank, self.dr, self.w_qn, self.w_kvn, self.eps, tables,
                                        ctx.tok_pos, ctx.err, append=None if after else append)
+        # the step's rows by the pool they go to, for the layers of this step that read this layer's cache
+        shared = ctx.__dict__.setdefault("step_rows", {})
+        if kv.writable:
+            shared[kv.k.data_ptr()] = rows
+        step_rows = shared.get(kv.k.data_ptr())
+        if (self.w_kv_heads is not None and kernels.ops.MMA_ATTENTION and not ctx.is_decode and step_rows is not None
+                and step_rows.shape[0] == x.shape[0] and not any(ctx.lens_before)):
+            heads = self._whole_prompts(cq, step_rows, tables, kv, ctx)
+            if after:
+                kernels.latent_append(rows, ctx.tok_pos, append)
+            if self.head_gate:
+                kernels.head_gate_(heads, proj[:, self.gate_off:], self.nh)
+            return kernels.linear(heads, self.w_o, out_dtype=_delta_dtype(heads))
         q = kernels.linear(cq, self.w_uq)
         q_lat = kernels.head_matmul(q, self.w_uk, tail=self.dr, tables=tables, tok_pos=ctx.tok_pos, err=ctx.err)
         o_lat = kernels.latent_attention(ctx.is_decode, q_lat, self.nh, self.row, self.kv_rank, rows if after else None, kv.k,
@@ -129,4 +163,22 @@ class LatentAttention(Mixer):
         if after:
             kernels.latent_append(rows, ctx.tok_pos, append)
         heads = kernels.head_matmul(o_lat, self.w_uv_t, gate=proj[:, self.gate_off:] if self.head_gate else None)
-        return kernels.linear(heads, self.w_o, out_dtype=torch.float32)
+        return kernels.linear(heads, self.w_o, out_dtype=_delta_dtype(heads))
+
+    def _whole_prompts(self, cq, rows, tables, kv, ctx):
+        """Attention of a step without history on the tensor cores: [T, heads * value_dim], before gate and output."""
+        H, dk = self.nh, self.dn + self.dr
+        packed = torch.empty((cq.shape[0], 3 * H * dk), dtype=cq.dtype, device=cq.device)     # queries | keys | values, by head
+        kernels.linear(cq, self.w_uq, out=packed[:, :H * dk])
+        kernels.rope_pairs_(packed, H, dk, self.dn, tables, ctx.tok_pos, ctx.err)
+        kernels.linear(rows, self.w_kv_heads, out=packed[:, H * dk:])
+        extras = kernels.AttnExtras(sink_logits=self.sink_logits) if self.sink else None
+        return kernels.attention_prefill(packed, H, H, dk, kv.k, kv.k, kv.page_table, kv.ring, ctx.seq_start, ctx.seq_len_before,
+                                         ctx.n_seqs, ctx.max_new, self.window, self.scale, all_from_cache=False, extras=extras)
+
+
+def _delta_dtype(x):
+    """What a part's last product hands on: float32 (the norm of the output reads it unrounded), except for many tokens
+    in bfloat16, where the paired-SM product (bfloat16 output) is the faster kernel."""
+    from .mlp import delta_dtype
+    return delta_dtype(x)

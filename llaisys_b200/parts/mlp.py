@@ -53,8 +53,8 @@ class SwiGLUMLP(FeedForward):
 class GatedMLP(FeedForward):
     """down(act(gate(x)) * up(x)), no biases, with the activation a parameter: "silu", "relu" or "gelu_tanh".  The gate
     and up matrices are kept as one [2I, H] matrix so that one product serves both; the activation and the product of
-    the halves are one pass in float32.  The result is returned in float32 (it may be normed before it joins the
-    stream).  params: hidden_size, intermediate_size, act, names (local tensor names of gate, up, down)."""
+    the halves are one pass in float32.  The result is returned in float32 for up to 256 tokens (it may be normed
+    before it joins the stream).  params: hidden_size, intermediate_size, act, names (local tensor names of gate, up, down)."""
     capturable = True
 
     def __init__(self, spec, env):
@@ -82,4 +82,10 @@ class GatedMLP(FeedForward):
             act = kernels.linear_swiglu(x, self.gate_up)
         else:
             act = kernels.glu(kernels.linear(x, self.gate_up), self.act)
-        return kernels.linear(act, self.down, out_dtype=torch.float32)
+        return kernels.linear(act, self.down, out_dtype=delta_dtype(act))
+
+
+def delta_dtype(x):
+    """The dtype in which a part hands its output to a norm that follows it: float32 (the norm reads it unrounded),
+    except for more than 256 tokens in bfloat16, where the paired-SM product (bfloat16 output) is the faster kernel."""
+    return torch.float32 if (x.dtype == torch.float32 or x.shape[0] <= 256) else x.dtype
