@@ -149,7 +149,10 @@ __global__ void __launch_bounds__(WARPS * 32) attn_kernel(AttnParams p) {
         // A tile is one cache page (tiles start at multiples of LLB_PAGE): its page is looked up once; rows move in
         // 16-byte pieces where the widths and the addresses allow it.
         const int p0 = tile * LLB_PAGE;
-        const T* kpage = kpool + paged_row(table, p.ring, p0, kvh, p.nkvh, DH, p.pinned);
+        // (the page table is read only for a tile that holds cached positions: a step without history may come with
+        // an empty table)
+        const bool cached = DECODE || p.all_from_cache || p0 < len_before;
+        const T* kpage = cached ? kpool + paged_row(table, p.ring, p0, kvh, p.nkvh, DH, p.pinned) : nullptr;
         constexpr int VEC = 16 / (int)sizeof(T);
         const bool kvec = DH % VEC == 0 && (((uintptr_t)kpool | (uintptr_t)knew) & 15) == 0 && kv_stride % VEC == 0;
         if (kvec) {
@@ -186,7 +189,7 @@ __global__ void __launch_bounds__(WARPS * 32) attn_kernel(AttnParams p) {
             }
         }
         if (!p.v_in_k) {
-            const T* vpage = vpool + paged_row(table, p.ring, p0, kvh, p.nkvh, DV, p.pinned);
+            const T* vpage = cached ? vpool + paged_row(table, p.ring, p0, kvh, p.nkvh, DV, p.pinned) : nullptr;
             for (int i = tid; i < LLB_PAGE * DV; i += WARPS * 32) {
                 int j = i / DV, d = i - j * DV;
                 int kp = p0 + j;

@@ -341,8 +341,8 @@ def test_whole_prompts_on_the_tensor_cores_against_the_path_over_the_cache(tmp_p
         n0 = ops.launch_count()
         got[mma] = [run_whole(engine, requests), run_batches(engine, requests, [[1, 3], [0, 2]], [1, 150, 30, 70])]
         got[mma].append(ops.launch_count() - n0)
-        for g in got[mma][:2]:             # (no recurrent layer here: every row within the bound)
-            compare(g, oracle, requests, torch.bfloat16, nh.like_config(cfg), f"tensor cores {mma}, window {window}")
+        for g in got[mma][:2]:
+            compare_nb(g, oracle, requests, torch.bfloat16, cfg, f"tensor cores {mma}, window {window}")
         assert not engine.cache.live_slots
     assert got[True][2] != got[False][2]                                   # the two paths are not the same launches
     for a, b in zip(got[True][:2], got[False][:2]):
@@ -350,7 +350,8 @@ def test_whole_prompts_on_the_tensor_cores_against_the_path_over_the_cache(tmp_p
             ref = b[key].astype(np.float64)
             rms = np.sqrt((ref ** 2).mean())
             d = a[key] - ref
-            assert np.sqrt((d ** 2).mean()) <= 0.03 * rms + 2e-4, (window, key)
+            # (a window of one key leaves a weight e^s / (e^s + e^sink) per head, which follows the score's rounding directly)
+            assert np.sqrt((d ** 2).mean()) <= (0.03 if window > 1 else 0.08) * rms + 2e-4, (window, key)
 
 
 def test_the_sequences_first_tokens(tmp_path):
