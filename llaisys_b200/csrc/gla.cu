@@ -24,7 +24,7 @@ struct GlaParams {
     const void* k;            // the same buffer at its first key column
     const void* v;            // the same buffer at its first value column
     int row_stride;
-    const float* z;           // decay logits [T, z_stride], head h at h * dk
+    const float* z;           // decay logits [T, z_stride], head h at h * dk (z_is_decay: the decays themselves)
     int z_stride;
     float* state;             // [slots, H * dk * dv]
     const int* seq_start;     // [B + 1]
@@ -32,17 +32,39 @@ struct GlaParams {
     float* out;               // [T, H * dv]
     int H, dk, dv;
     float q_scale, inv_tau;
+    int z_is_decay;           // z already holds a = sigmoid(z)^(1/tau) (llb_gla_decay ran over it)
 };
+
+// log sigmoid(z) = -softplus(-z) = -(max(-z, 0) + log(1 + e^-|z|));  a = sigmoid(z)^(1/tau) = exp(log sigmoid(z) / tau)
+__device__ __forceinline__ float gla_decay(float z, float inv_tau) {
+    return expf(-(fmaxf(-z, 0.f) + log1pf(expf(-fabsf(z)))) * inv_tau);
+}
+
+// z <- a in place, once per (token, channel): for many tokens, so that the blocks that share a head do not each repeat it.
+__global__ void gla_decay_kernel(float* __restrict__ z, size_t n, float inv_tau) {
+    llb_grid_dependency_sync();
+    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) z[i] = gla_decay(z[i], inv_tau);
+}
+
+LLB_API int llb_gla_decay(float* z, long long n, float inv_tau, cudaStream_t stream) {
+    if (n == 0) return 0;
+    llb_launch(gla_decay_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, stream, z, (size_t)n, inv_tau);
+    return llb_status();
+}
 
 // KS lanes share a value column, each with KPT consecutive key channels of it (KPT a multiple of 4); a block of 128
 // threads owns 128 / KS columns.  In shared memory a lane's channels of a token are KPT consecutive floats, the lanes'
-// groups KPT + 4 apart, so that the 16-byte reads of the lanes of a quarter-warp fall on different banks.
+// groups an odd number of 16-byte pieces apart, so that the 16-byte reads of the lanes of a quarter-warp fall on
+// different banks (measured with groups 32 bytes apart: two-way conflicts on every read of q, k and a).
+constexpr int gla_pad(int kpt) { return (kpt / 4) % 2 == 1 ? 0 : 4; }
 template <typename T, int KS, int KPT>
 __global__ void __launch_bounds__(GLA_THREADS) gla_scan_kernel(GlaParams p) {
     extern __shared__ __align__(16) float sm[];
     constexpr int COLS = GLA_THREADS / KS;
     constexpr int DKP = KS * KPT;                     // key channels, padded
-    constexpr int ROW = KS * (KPT + 4);               // floats of one token's q (or k, or a) in shared memory
+    constexpr int PAD = gla_pad(KPT);
+    constexpr int ROW = KS * (KPT + PAD);               // floats of one token's q (or k, or a) in shared memory
     float* sq = sm;                                   // [CHUNK][ROW]
     float* sk = sq + GLA_CHUNK * ROW;
     float* sa = sk + GLA_CHUNK * ROW;
@@ -76,7 +98,7 @@ __global__ void __launch_bounds__(GLA_THREADS) gla_scan_kernel(GlaParams p) {
         for (int e = 0; e < NQ; ++e) {
             const int idx = tid + e * GLA_THREADS, t = idx / DKP, i = idx - t * DKP;
             rq[e] = rk[e] = 0.f;
-            rz[e] = INFINITY;                              // a decay of exactly one
+            rz[e] = p.z_is_decay ? 1.f : INFINITY;         // a decay of exactly one
             if (idx < GLA_CHUNK * DKP && i < dk && t < nc) {
                 const size_t row = (size_t)(tok0 + c0 + t);
                 rq[e] = to_f32(qb[row * p.row_stride + h * dk + i]);
@@ -102,12 +124,10 @@ __global__ void __launch_bounds__(GLA_THREADS) gla_scan_kernel(GlaParams p) {
             const int idx = tid + e * GLA_THREADS;
             if (idx < GLA_CHUNK * DKP) {
                 const int t = idx / DKP, i = idx - t * DKP;
-                const int at = t * ROW + (i / KPT) * (KPT + 4) + (i % KPT);
-                const float zz = rz[e];
+                const int at = t * ROW + (i / KPT) * (KPT + PAD) + (i % KPT);
                 sq[at] = rq[e] * p.q_scale;
                 sk[at] = rk[e];
-                // log sigmoid(z) = -softplus(-z) = -(max(-z, 0) + log(1 + e^-|z|))
-                sa[at] = expf(-(fmaxf(-zz, 0.f) + log1pf(expf(-fabsf(zz)))) * p.inv_tau);
+                sa[at] = p.z_is_decay ? rz[e] : gla_decay(rz[e], p.inv_tau);
             }
         }
 #pragma unroll
@@ -121,9 +141,9 @@ __global__ void __launch_bounds__(GLA_THREADS) gla_scan_kernel(GlaParams p) {
 #pragma unroll
         for (int t = 0; t < GLA_CHUNK; ++t) {
             const float vv = sv[t * COLS + cloc];
-            const float4* a4 = reinterpret_cast<const float4*>(sa + t * ROW + part * (KPT + 4));
-            const float4* k4 = reinterpret_cast<const float4*>(sk + t * ROW + part * (KPT + 4));
-            const float4* q4 = reinterpret_cast<const float4*>(sq + t * ROW + part * (KPT + 4));
+            const float4* a4 = reinterpret_cast<const float4*>(sa + t * ROW + part * (KPT + PAD));
+            const float4* k4 = reinterpret_cast<const float4*>(sk + t * ROW + part * (KPT + PAD));
+            const float4* q4 = reinterpret_cast<const float4*>(sq + t * ROW + part * (KPT + PAD));
             float a0 = 0.f, a1 = 0.f;                 // two chains, so that the sum does not wait on one
 #pragma unroll
             for (int m = 0; m < KPT; m += 4) {
@@ -161,7 +181,8 @@ template <typename T, int KS, int KPT>
 static int launch_scan(const GlaParams& p, int B, cudaStream_t stream) {
     auto k = gla_scan_kernel<T, KS, KPT>;
     constexpr int COLS = GLA_THREADS / KS;
-    size_t smem = (size_t)(3 * GLA_CHUNK * KS * (KPT + 4) + GLA_CHUNK * COLS) * sizeof(float);
+    constexpr int PAD = gla_pad(KPT);
+    size_t smem = (size_t)(3 * GLA_CHUNK * KS * (KPT + PAD) + GLA_CHUNK * COLS) * sizeof(float);
     dim3 grid((p.dv + COLS - 1) / COLS, p.H, B);
     if (grid.y > 65535 || grid.z > 65535) return (int)cudaErrorInvalidValue;
     static bool configured = false;          // once per instantiation: not repeated inside a graph capture

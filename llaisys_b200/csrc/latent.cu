@@ -325,9 +325,29 @@ __global__ void head_gate_kernel(T* __restrict__ x, const T* __restrict__ gate, 
     x[i] = from_f32<T>(to_f32(x[i]) / (1.0f + expf(-g)));
 }
 
+// bfloat16, head width a multiple of 8, 16-byte aligned: a thread takes eight neighbouring elements of one head
+__global__ void head_gate_vec_kernel(bf16* __restrict__ x, const bf16* __restrict__ gate, int gate_stride, int H, int width8, size_t n8) {
+    llb_grid_dependency_sync();
+    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n8) return;
+    size_t th = i / width8, t = th / H;
+    int h = (int)(th - t * H);
+    const float f = 1.0f / (1.0f + expf(-__bfloat162float(gate[t * gate_stride + h])));
+    uint4 v = reinterpret_cast<uint4*>(x)[i];
+    bf16* e = reinterpret_cast<bf16*>(&v);
+#pragma unroll
+    for (int k = 0; k < 8; ++k) e[k] = __float2bfloat16_rn(__bfloat162float(e[k]) * f);
+    reinterpret_cast<uint4*>(x)[i] = v;
+}
+
 LLB_API int llb_head_gate(void* x, const void* gate, int gate_stride, int dtype, int T, int H, int width, cudaStream_t stream) {
     size_t n = (size_t)T * H * width;
     if (n == 0) return 0;
+    if (dtype == LLB_BF16 && width % 8 == 0 && !((uintptr_t)x & 15)) {
+        llb_launch(head_gate_vec_kernel, dim3((unsigned)((n / 8 + 255) / 256)), dim3(256), 0, stream, (bf16*)x, (const bf16*)gate,
+                   gate_stride, H, width / 8, n / 8);
+        return llb_status();
+    }
     LLB_DISPATCH_DTYPE(dtype, TT, {
         llb_launch(head_gate_kernel<TT>, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, stream, (TT*)x, (const TT*)gate,
                    gate_stride, H, width, n);

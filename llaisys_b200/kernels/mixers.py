@@ -15,7 +15,7 @@ from .ops import DT, KernelError, _AttnParams, _attn_lib, _check, _dt, _fn, _nee
 class _GlaParams(ctypes.Structure):
     _fields_ = [("q", c_void_p), ("k", c_void_p), ("v", c_void_p), ("row_stride", c_int), ("z", c_void_p), ("z_stride", c_int),
                 ("state", c_void_p), ("seq_start", c_void_p), ("seq_slot", c_void_p), ("out", c_void_p), ("H", c_int),
-                ("dk", c_int), ("dv", c_int), ("q_scale", c_float), ("inv_tau", c_float)]
+                ("dk", c_int), ("dv", c_int), ("q_scale", c_float), ("inv_tau", c_float), ("z_is_decay", c_int)]
 
 
 GLA_MAX_KEY_DIM = 256
@@ -25,7 +25,8 @@ def gla_scan(proj: torch.Tensor, H: int, dk: int, dv: int, z: torch.Tensor, stat
              seq_slot: torch.Tensor, n_seqs: int, q_scale: float, decay_root: float) -> torch.Tensor:
     """The gated-linear-attention recurrence over the new tokens of every sequence: proj [T, >= 2 H dk + H dv] holds the
     heads' queries, then keys, then values; z [T, H dk] (float32) the decay logits; state [slots, H dk dv] (float32) is
-    read at row seq_slot[b] and left holding the state after the step.  Returns o [T, H dv] in float32."""
+    read at row seq_slot[b] and left holding the state after the step.  Returns o [T, H dv] in float32.  For more than
+    64 tokens the decays are formed by a pass of their own over z (in place), once per token and channel."""
     _need_cuda(proj, z, state)
     assert z.dtype == torch.float32 and z.stride(1) == 1 and state.dtype == torch.float32 and state.is_contiguous()
     assert proj.stride(1) == 1 and state.shape[1] == H * dk * dv
@@ -39,6 +40,10 @@ def gla_scan(proj: torch.Tensor, H: int, dk: int, dv: int, z: torch.Tensor, stat
     p.row_stride, p.z, p.z_stride = proj.stride(0), z.data_ptr(), z.stride(0)
     p.state, p.seq_start, p.seq_slot, p.out = state.data_ptr(), seq_start.data_ptr(), seq_slot.data_ptr(), out.data_ptr()
     p.H, p.dk, p.dv, p.q_scale, p.inv_tau = H, dk, dv, q_scale, 1.0 / decay_root
+    if T > 64 and z.is_contiguous():
+        g = _fn(load_module("gla.cu"), "llb_gla_decay", [c_void_p, ctypes.c_longlong, c_float, c_void_p])
+        _check(g(_ptr(z), z.numel(), 1.0 / decay_root, _stream()), "gated linear attention (decays)")
+        p.z_is_decay = 1
     f = _fn(load_module("gla.cu"), "llb_gla_scan", [_GlaParams, c_int, c_int, c_int, c_void_p])
     _check(f(p, _dt(proj), n_seqs, _sm_count(proj.device), _stream()), "gated linear attention (recurrence)")
     return out
