@@ -213,13 +213,26 @@ __global__ void __launch_bounds__(WARPS * 32) attn_kernel(AttnParams p) {
             const float* qr = Qs + r * DH;
             const float* k0 = Ks + lane * (DH + 1);
             const float* k1 = Ks + (lane + 32) * (DH + 1);
-            float s0 = 0.f, s1 = 0.f;
-#pragma unroll 8
-            for (int d = 0; d < DH; ++d) {
-                float qv = qr[d];
-                s0 = fmaf(qv, k0[d], s0);
-                s1 = fmaf(qv, k1[d], s1);
+            // four partial sums a key: eight independent chains, so that a product does not wait for the one before it
+            // (with one chain a key the warp spent most cycles on the latency of its own additions)
+            float a0[4] = {0.f, 0.f, 0.f, 0.f}, a1[4] = {0.f, 0.f, 0.f, 0.f};
+            {
+                int d = 0;
+#pragma unroll 4
+                for (; d + 4 <= DH; d += 4) {
+#pragma unroll
+                    for (int u = 0; u < 4; ++u) {
+                        float qv = qr[d + u];
+                        a0[u] = fmaf(qv, k0[d + u], a0[u]);
+                        a1[u] = fmaf(qv, k1[d + u], a1[u]);
+                    }
+                }
+                for (; d < DH; ++d) {
+                    a0[0] = fmaf(qr[d], k0[d], a0[0]);
+                    a1[0] = fmaf(qr[d], k1[d], a1[0]);
+                }
             }
+            float s0 = (a0[0] + a0[1]) + (a0[2] + a0[3]), s1 = (a1[0] + a1[1]) + (a1[2] + a1[3]);
             int kp0 = tile * LLB_PAGE + lane, kp1 = kp0 + 32;
             bool v0 = (kp0 >= lo || kp0 < keep) && kp0 <= pos, v1 = (kp1 >= lo || kp1 < keep) && kp1 <= pos;
             s0 = v0 ? s0 * p.scale : -INFINITY;
@@ -235,15 +248,16 @@ __global__ void __launch_bounds__(WARPS * 32) attn_kernel(AttnParams p) {
             ps[lane] = p0;
             ps[lane + 32] = p1;
             __syncwarp();
+            // keys outside, the lane's output dimensions inside: DPL independent chains
 #pragma unroll
-            for (int e = 0; e < DPL; ++e) {
-                int d = lane + e * 32;
-                if (d < DV) {
-                    float acc = o[i][e] * alpha;
-#pragma unroll 8
-                    for (int j = 0; j < LLB_PAGE; ++j) acc = fmaf(ps[j], Vs[j * vs_stride + d], acc);
-                    o[i][e] = acc;
-                }
+            for (int e = 0; e < DPL; ++e) o[i][e] *= alpha;
+#pragma unroll 4
+            for (int j = 0; j < LLB_PAGE; ++j) {
+                const float pj = ps[j];
+                const float* vr = Vs + j * vs_stride + lane;
+#pragma unroll
+                for (int e = 0; e < DPL; ++e)
+                    if (lane + e * 32 < DV) o[i][e] = fmaf(pj, vr[e * 32], o[i][e]);
             }
         }
     }
