@@ -156,23 +156,34 @@ __global__ void __launch_bounds__(WARPS * 32) attn_kernel(AttnParams p) {
         constexpr int VEC = 16 / (int)sizeof(T);
         const bool kvec = DH % VEC == 0 && (((uintptr_t)kpool | (uintptr_t)knew) & 15) == 0 && kv_stride % VEC == 0;
         if (kvec) {
-            for (int i = tid; i < LLB_PAGE * (DH / VEC); i += WARPS * 32) {
-                int j = i / (DH / VEC), d = (i - j * (DH / VEC)) * VEC;
-                int kp = p0 + j;
-                float vals[VEC];
+            // eight pieces a thread are requested before the first is used: the walk waits for memory once per batch
+            constexpr int PIECES = LLB_PAGE * (DH / VEC), BATCH = 8;
+            for (int i0 = tid; i0 < PIECES; i0 += BATCH * WARPS * 32) {
+                uint4 raw[BATCH];
 #pragma unroll
-                for (int e = 0; e < VEC; ++e) vals[e] = 0.f;
-                if ((kp >= key_lo || kp < keep) && kp <= last_pos) {
-                    const T* src = (!DECODE && !p.all_from_cache && kp >= len_before)
-                                       ? knew + (size_t)(tok0 + kp - len_before) * kv_stride + kvh * DH + d
-                                       : kpage + (size_t)j * DH + d;
-                    const uint4 raw = *reinterpret_cast<const uint4*>(src);
-                    const T* rv = reinterpret_cast<const T*>(&raw);
-#pragma unroll
-                    for (int e = 0; e < VEC; ++e) vals[e] = to_f32(rv[e]);
+                for (int u = 0; u < BATCH; ++u) {
+                    const int i = i0 + u * WARPS * 32;
+                    raw[u] = make_uint4(0u, 0u, 0u, 0u);                 // zero bits are zero in both types
+                    if (i < PIECES) {
+                        const int j = i / (DH / VEC), d = (i - j * (DH / VEC)) * VEC, kp = p0 + j;
+                        if ((kp >= key_lo || kp < keep) && kp <= last_pos) {
+                            const T* src = (!DECODE && !p.all_from_cache && kp >= len_before)
+                                               ? knew + (size_t)(tok0 + kp - len_before) * kv_stride + kvh * DH + d
+                                               : kpage + (size_t)j * DH + d;
+                            raw[u] = *reinterpret_cast<const uint4*>(src);
+                        }
+                    }
                 }
 #pragma unroll
-                for (int e = 0; e < VEC; ++e) Ks[j * (DH + 1) + d + e] = vals[e];
+                for (int u = 0; u < BATCH; ++u) {
+                    const int i = i0 + u * WARPS * 32;
+                    if (i < PIECES) {
+                        const int j = i / (DH / VEC), d = (i - j * (DH / VEC)) * VEC;
+                        const T* rv = reinterpret_cast<const T*>(&raw[u]);
+#pragma unroll
+                        for (int e = 0; e < VEC; ++e) Ks[j * (DH + 1) + d + e] = to_f32(rv[e]);
+                    }
+                }
             }
         } else {
             for (int i = tid; i < LLB_PAGE * DH; i += WARPS * 32) {

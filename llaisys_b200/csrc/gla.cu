@@ -212,7 +212,9 @@ static int launch_scan_ks(const GlaParams& p, int B, cudaStream_t stream) {
 
 // Runs the recurrence over the new tokens of every sequence of the step and writes o [T, H * dv] (float32).
 // sms: multiprocessors of the device.  More lanes share a column (fewer columns a block, more blocks) while the blocks
-// would not fill the device and a lane still keeps four channels or more.
+// would not fill the device and a lane still keeps four channels or more.  (Splitting further was measured and lost:
+// 32 heads of 128 x 128 over 2,048 tokens took 800 us with 8 lanes a column and 867 us with 16; every lane reads its
+// share of q, k and a from shared memory for every token, and that traffic, not the arithmetic, sets the pace.)
 LLB_API int llb_gla_scan(GlaParams p, int dtype, int B, int sms, cudaStream_t stream) {
     if (B == 0) return 0;
     if (p.dk <= 0 || p.dv <= 0 || p.H <= 0 || p.dk > 256) return (int)cudaErrorInvalidValue;
