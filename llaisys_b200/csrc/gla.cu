@@ -212,9 +212,10 @@ static int launch_scan_ks(const GlaParams& p, int B, cudaStream_t stream) {
 
 // Runs the recurrence over the new tokens of every sequence of the step and writes o [T, H * dv] (float32).
 // sms: multiprocessors of the device.  More lanes share a column (fewer columns a block, more blocks) while the blocks
-// would not fill the device and a lane still keeps four channels or more.  (Splitting further was measured and lost:
-// 32 heads of 128 x 128 over 2,048 tokens took 800 us with 8 lanes a column and 867 us with 16; every lane reads its
-// share of q, k and a from shared memory for every token, and that traffic, not the arithmetic, sets the pace.)
+// would not fill the device and a lane still keeps four channels or more.  (Measured and lost at 32 heads of 128 x 128
+// over 2,048 tokens, 800 us as it is: splitting further, 16 lanes a column, 867 us; four columns a lane, so that what a
+// lane reads of q, k and a serves four columns, 1,129 us with a quarter of the blocks.  The walk is bound by latency
+// at one warp a scheduler, about 120 instructions a token and warp, not by shared memory or arithmetic.)
 LLB_API int llb_gla_scan(GlaParams p, int dtype, int B, int sms, cudaStream_t stream) {
     if (B == 0) return 0;
     if (p.dk <= 0 || p.dv <= 0 || p.H <= 0 || p.dk > 256) return (int)cudaErrorInvalidValue;

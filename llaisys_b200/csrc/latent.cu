@@ -198,9 +198,19 @@ __global__ void __launch_bounds__(HM_THREADS) head_matmul_kernel(HeadMatmulParam
     const int per = (p.n_in + HM_WARPS - 1) / HM_WARPS, d0 = warp * per, d1 = min(p.n_in, d0 + per);
     llb_grid_dependency_sync();
     const T* xb = (const T*)p.x;
-    for (int i = tid; i < HM_TOK * p.n_in; i += HM_THREADS) {
-        int t = i / p.n_in, d = i - t * p.n_in;
-        xs[i] = t < nt ? to_f32(xb[(size_t)(t0 + t) * p.x_stride + h * p.x_head + d]) : 0.f;
+    // the tile's inputs: four loads a thread are requested before the first is stored
+    for (int i0 = tid; i0 < HM_TOK * p.n_in; i0 += 4 * HM_THREADS) {
+        float v[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const int i = i0 + u * HM_THREADS, t = i / p.n_in, d = i - t * p.n_in;
+            v[u] = (i < HM_TOK * p.n_in && t < nt) ? to_f32(xb[(size_t)(t0 + t) * p.x_stride + h * p.x_head + d]) : 0.f;
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const int i = i0 + u * HM_THREADS;
+            if (i < HM_TOK * p.n_in) xs[i] = v[u];
+        }
     }
     __syncthreads();
     T* yb = (T*)p.y;
