@@ -109,7 +109,9 @@ def latent_attention_mixer(h, w, p, mix, eps, positions, kv):
     val = (c @ w[p + ".uv"].T).reshape(T, H, dv)
     s = (np.einsum("thd,shd->hts", q[:, :, :dn], kn) + np.einsum("thd,sd->hts", qr, kr)) * float(mix["scale"])
     i, j = np.asarray(positions)[:, None], np.asarray(positions)[None, :]
-    seen = (j <= i) & (i - j < int(mix["mask"]["size"]))
+    seen = j <= i
+    if mix.get("mask") is not None:
+        seen = seen & (i - j < int(mix["mask"]["size"]))
     s = np.where(seen[None], s, -np.inf)
     sink = np.asarray(w[p + ".sink"], dtype=np.float64)
     m = np.maximum(s.max(axis=-1), sink[:, None])

@@ -354,6 +354,22 @@ def test_whole_prompts_on_the_tensor_cores_against_the_path_over_the_cache(tmp_p
             assert np.sqrt((d ** 2).mean()) <= (0.03 if window > 1 else 0.08) * rms + 2e-4, (window, key)
 
 
+def test_latent_layers_without_a_window_and_without_rotation(tmp_path):
+    """No mask in the configuration: every earlier key is seen (own cache, and a reader of it); no rotated dimensions."""
+    cfg = nh.config(77, 40, [nh.latent(2, 8, 4, 6, 12, 10, 5, rot_dims=0), nh.latent(3, 4, 4, 8, 8, 10, 5, kv_from=0, rot_dims=0, ff=24),
+                             nh.latent(2, 6, 2, 4, 8, 6, 5, ff=16)], embed_scale=1.5, mult=0.9)
+    for layer in cfg["layers"]:
+        del layer["mixer"]["mask"]
+    folder = nh.make_folder(tmp_path, cfg, seed=8, gain=9.0)
+    oracle, requests = nh.Oracle(folder), nh.random_requests(cfg, [150, 3, 70], seed=4)
+    engine = build_engine(folder, torch.float32, max_tokens=64 * 6)
+    assert engine.cache.rings == [None, None] or engine.cache.rings == [None]
+    like = nh.like_config(cfg)
+    compare(run_whole(engine, requests), oracle, requests, torch.float32, like, "no window whole")
+    compare(run_tail_by_one(engine, requests, tail=80), oracle, requests, torch.float32, like, "no window decoded")
+    compare(run_batches(engine, requests, [[0, 1, 2]], [100, 1, 64]), oracle, requests, torch.float32, like, "no window together")
+
+
 def test_the_sequences_first_tokens(tmp_path):
     """One, two and three tokens: empty history, a state that starts at zero, a softmax over one key and the sink."""
     cfg = nh.CONFIGS["P"]
