@@ -34,7 +34,9 @@
 
 constexpr int DH = LLB_HEAD_DIM;     // query / key width
 constexpr int DV = LLB_VALUE_DIM;    // value and output width
-constexpr int ROWS = DH > 256 ? 8 : 32;   // query rows of a block (fewer for very wide keys, so that a tile still fits)
+// query rows of a block: 32, or 8 for keys so wide that 32 rows and a key tile no longer fit an SM's shared memory
+constexpr bool ROWS32_FIT = (size_t)(32 * DH + LLB_PAGE * (DH + 1) + 4 * LLB_PAGE) * sizeof(float) <= 227 * 1024;
+constexpr int ROWS = (DH <= 256 || ROWS32_FIT) ? 32 : 8;
 constexpr int WARPS = 4;
 constexpr int RPW = ROWS / WARPS;   // rows of a warp
 constexpr int DPL = (DV + 31) / 32; // output dims of a lane

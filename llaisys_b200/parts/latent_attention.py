@@ -178,7 +178,6 @@ class LatentAttention(Mixer):
 
 
 def _delta_dtype(x):
-    """What a part's last product hands on: float32 (the norm of the output reads it unrounded), except for many tokens
-    in bfloat16, where the paired-SM product (bfloat16 output) is the faster kernel."""
+    """What a part's last product hands on to the norm of its output (see parts/mlp.py: delta_dtype)."""
     from .mlp import delta_dtype
     return delta_dtype(x)

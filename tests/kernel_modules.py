@@ -9,7 +9,7 @@ TEST_MODULES = [
     *[("attention_simt.cu", {"LLB_HEAD_DIM": k, "LLB_VALUE_DIM": v}) for k, v in ((16, 24), (32, 16), (48, 32))],
     ("attention_simt.cu", {"LLB_HEAD_DIM": 18}), ("attention_simt.cu", {"LLB_HEAD_DIM": 7, "LLB_VALUE_DIM": 5}),
     # latent attention: cache rows (latent + rotated part) whose leading elements are the values (test_gpu_nubedra.py)
-    *[("attention_simt.cu", {"LLB_HEAD_DIM": k, "LLB_VALUE_DIM": v}) for k, v in ((40, 24), (48, 40), (28, 18), (28, 20), (9, 7), (272, 264), (32, 24), (56, 40), (14, 10), (8, 6))],
+    *[("attention_simt.cu", {"LLB_HEAD_DIM": k, "LLB_VALUE_DIM": v}) for k, v in ((40, 24), (48, 40), (28, 18), (28, 20), (9, 7), (272, 264), (32, 24), (56, 40), (14, 10), (8, 6), (600, 560))],
     # the build in which a bounded wait can be made to run out (test_gpu_kernels.py)
     ("gemm_tc.cu", {"LLB_WAIT_LIMIT": 4096, "LLB_TEST_STALL": 1}),
 ]

@@ -276,11 +276,12 @@ def test_latent_attention_alone_keys_at_the_windows_edge(dtype, window):
             assert np.abs(got[0] - want[-1]).max() < tol and np.abs(got[1] - want2[0]).max() < tol, ("token", ring, splits)
 
 
-def test_latent_attention_rows_wider_than_a_block_of_queries_allows():
-    """Cache rows of more than 256 elements run with fewer query rows a block."""
+@pytest.mark.parametrize("sizes", [(272, 264), (600, 560)])
+def test_latent_attention_rows_wider_than_a_block_of_queries_allows(sizes):
+    """Cache rows of more than 256 elements; the widest run with fewer query rows a block."""
     from llaisys_b200 import kernels
     rng = np.random.default_rng(12)
-    H, width, vw, L = 3, 272, 264, 150
+    (width, vw), H, L = sizes, 3, 150
     rows = _bf16_exact(rng.normal(size=(L, width)) * 0.3)
     q = _bf16_exact(rng.normal(size=(L, H, width)) * 0.4)
     sink = np.zeros(H)
