@@ -371,6 +371,19 @@ def test_latent_layers_without_a_window_and_without_rotation(tmp_path):
     compare(run_batches(engine, requests, [[0, 1, 2]], [100, 1, 64]), oracle, requests, torch.float32, like, "no window together")
 
 
+def test_a_model_of_recurrent_layers_only(tmp_path):
+    """No layer keeps keys: the cache has no page groups at all, only state rows."""
+    cfg = nh.config(61, 24, [nh.gla(2, 8, 12, 3.0, ff=32), nh.gla(3, 4, 8, 20.0)], embed_scale=1.2, mult=0.75)
+    for dtype in DTYPES:
+        folder = nh.make_folder(tmp_path / str(dtype), cfg, seed=6, gain=nh.GAIN[dtype])
+        oracle, requests = nh.Oracle(folder), nh.random_requests(cfg, [90, 2, 40], seed=3)
+        engine = build_engine(folder, dtype, max_tokens=64 * 4)
+        assert engine.cache.group_keys == []
+        compare_nb(run_whole(engine, requests), oracle, requests, dtype, cfg, "recurrent only whole")
+        compare_nb(run_batches(engine, requests, [[0, 1, 2]], [30, 1, 40]), oracle, requests, dtype, cfg, "recurrent only together")
+        assert not engine.cache.live_slots
+
+
 def test_the_sequences_first_tokens(tmp_path):
     """One, two and three tokens: empty history, a state that starts at zero, a softmax over one key and the sink."""
     cfg = nh.CONFIGS["P"]
